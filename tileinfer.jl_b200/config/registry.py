@@ -14,6 +14,7 @@ from typing import Any, Callable, Dict, Mapping, Optional
 
 from .apertus import ApertusConfig, ConfigError
 from .vogilix import VogilixConfig
+from .sozanex import SozanexConfig
 from .zudepel import ZudepelConfig
 
 
@@ -73,3 +74,4 @@ def load_config(model_dir: str):
 register_architecture(ApertusConfig.architecture, ApertusConfig, model_type=ApertusConfig.model_type)
 register_architecture(VogilixConfig.architecture, VogilixConfig, model_type=VogilixConfig.model_type)
 register_architecture(ZudepelConfig.architecture, ZudepelConfig, model_type=ZudepelConfig.model_type)
+register_architecture(SozanexConfig.architecture, SozanexConfig, model_type=SozanexConfig.model_type)

@@ -44,19 +44,31 @@ class Llama3RopeScaling:
 
 
 @dataclass(frozen=True)
+class YarnRopeScaling:
+    """YaRN scaling of the rotation's frequencies: pair i of ``dims / 2`` keeps its frequency below the pair index ``lo``,
+    takes frequency / factor above ``hi`` and a linear blend between, where lo and hi are the (fractional) pair indices
+    whose wavelengths fit ``fast`` and ``slow`` times into ``original`` positions; cos and sin are multiplied by
+    ``0.1 ln(factor) + 1``."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class PositionSpec:
     """Position encoding applied inside a mixer. ``kind`` selects the registered part."""
     kind: str                      # "rope" | "none" | user-registered
     head_dim: int = 0
     theta: float = 10000.0
-    scaling: Optional[Llama3RopeScaling] = None
+    scaling: Optional[Any] = None  # Llama3RopeScaling | YarnRopeScaling
     max_positions: int = 0
     options: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str                      # "rmsnorm" | "rmsnorm32" (options: "offset": the checkpoint keeps w - 1)
+    kind: str                      # "rmsnorm" | "rmsnorm32" (options: "offset": the checkpoint keeps w - 1) | "layernorm32"
     size: int
     eps: float
     weight_name: str               # checkpoint tensor name (full)
@@ -120,13 +132,29 @@ class TokenInputSpec:
 class LayerSpec:
     """``feed_forward`` (with its norm) may be None: a layer that only mixes. ``token_input``: a part that adds
     something of the token itself to the stream at the end of the layer, for the blocks that know of it.
-    ``options``: constants of the arrangement (a multiplier of the residual branches, for one)."""
-    block: str                     # arrangement: "pre_norm" | "post_norm"
+    ``options``: constants of the arrangement (a multiplier of the residual branches, for one). ``mixer_post_norm`` and
+    ``feed_forward_post_norm``: a second norm per sublayer, on its output, for the arrangement that has a norm on both sides
+    ("sandwich")."""
+    block: str                     # arrangement: "pre_norm" | "post_norm" | "parallel" | "sandwich"
     mixer: MixerSpec
     mixer_norm: NormSpec
     feed_forward: Optional[FeedForwardSpec]
     feed_forward_norm: Optional[NormSpec]
     token_input: Optional[TokenInputSpec] = None
+    options: Mapping[str, Any] = field(default_factory=dict)
+    mixer_post_norm: Optional[NormSpec] = None
+    feed_forward_post_norm: Optional[NormSpec] = None
+
+
+@dataclass(frozen=True)
+class PassInputSpec:
+    """Something that rewrites the residual stream from the stream and the embedding's output before some of the layer runs
+    (the first layer of every pass of a stretch of layers that runs several times with the same weights). ``kind`` selects
+    the registered part; ``at``: the positions in ``ModelSpec.order`` before which it runs."""
+    kind: str                      # "concat_linear" | user-registered
+    hidden_size: int
+    weight_name: str
+    at: Tuple[int, ...]
     options: Mapping[str, Any] = field(default_factory=dict)
 
 
@@ -152,3 +180,4 @@ class ModelSpec:
     embedding_kind: str = "lookup"
     head_kind: str = "linear"
     options: Mapping[str, Any] = field(default_factory=dict)
+    pass_input: Optional[PassInputSpec] = None

@@ -154,14 +154,21 @@ __device__ __forceinline__ void xielu_bf16_pair(float s0, float s1, const XieluP
 }
 
 // GELU in its exact form 0.5 x (1 + erf(x / sqrt 2)) and in its tanh form 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))).
-// As a product's epilogue (codes TI_EPI_GELU_ERF / TI_EPI_GELU_TANH) it is applied to the sum rounded to the storage type.
+// As a product's epilogue (codes TI_EPI_GELU_ERF / TI_EPI_GELU_TANH) it is applied to the sum rounded to the storage type; so is
+// the squared rectifier max(x, 0)^2 (TI_EPI_RELU2).
 #define TI_EPI_GELU_ERF 4
 #define TI_EPI_GELU_TANH 5
+#define TI_EPI_RELU2 6
+#define TI_EPI_LAST TI_EPI_RELU2
 __device__ __forceinline__ float gelu_erf_value(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
 __device__ __forceinline__ float gelu_tanh_value(float z) {
     return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
 }
 __device__ __forceinline__ float gelu_epilogue(float v, int epilogue) {
+    if (epilogue == TI_EPI_RELU2) {
+        const float r = fmaxf(v, 0.f);
+        return r * r;
+    }
     return epilogue == TI_EPI_GELU_TANH ? gelu_tanh_value(v) : gelu_erf_value(v);
 }
 

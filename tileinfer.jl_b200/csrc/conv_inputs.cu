@@ -3,6 +3,7 @@
 //   u_t = T(W h_t + b)                                    the projection's row (the product comes rounded to T; the bias is added here)
 //   y_t[c] = T( sum_j conv[c][j] * u_(t - taps + 1 + j)[c] )   zeros before the sequence's start
 //   q, k  <- y / rms(y over the WHOLE row of q, or of k) * w    (weights as long as the row; optional)
+//            or, with head_norm, every head by itself: y_h / rms(y_h) * w, one weight of the head's size for all heads
 //   q, k  <- rotation of the first `rotary` elements of every head by the position's angles (optional)
 //   q -> q_out [n, heads, Dp]; k, v -> their place in the paged cache [pages][kv_heads][page][Dp]
 //
@@ -32,7 +33,7 @@ __global__ void __launch_bounds__(CI_THREADS) conv_attention_inputs_kernel(
     const T* __restrict__ q_norm_w, const T* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_sin, int rotary,
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* positions, const int* slot_map,
     const int* cu_seqlens, const int* seq_slots, const int* kv_lens, int B, int nq, int nkv, int D, int V, int Dp, int page_size,
-    int write_kv) {
+    int write_kv, int head_norm) {
     extern __shared__ float y[];                       // [channels]
     __shared__ float scratch[33];
     const int t = blockIdx.x;
@@ -81,6 +82,22 @@ __global__ void __launch_bounds__(CI_THREADS) conv_attention_inputs_kernel(
         if (c < Cq) ssq = fmaf(acc, acc, ssq);
         else if (c < Cq + Ck) ssk = fmaf(acc, acc, ssk);
     }
+    if (head_norm) {
+        // A warp per head: the order of a head's sum depends on the head's size alone.
+        __syncthreads();
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int heads = nq + (write_kv ? nkv : 0);
+        for (int hd = warp; hd < heads; hd += CI_THREADS / 32) {
+            const T* w = hd < nq ? q_norm_w : k_norm_w;
+            if (w == nullptr) continue;
+            float* src = y + (size_t)hd * D;
+            float ss = 0.f;
+            for (int d = lane; d < D; d += 32) ss = fmaf(src[d], src[d], ss);
+            const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+            for (int d = lane; d < D; d += 32) src[d] = src[d] * inv * to_f32(w[d]);
+        }
+        q_norm_w = k_norm_w = nullptr;         // done; the whole-row norm below is skipped
+    }
     float invq = 1.f, invk = 1.f;
     if (q_norm_w != nullptr) invq = 1.0f / sqrtf(block_sum(ssq, scratch) / (float)Cq + eps);
     if (k_norm_w != nullptr && write_kv) invk = 1.0f / sqrtf(block_sum(ssk, scratch) / (float)Ck + eps);
@@ -120,12 +137,13 @@ __global__ void __launch_bounds__(CI_THREADS) conv_attention_inputs_kernel(
 
 // proj [n, ld] of T: the step's projected rows, queries (nq * D) then, with write_kv, keys (nkv * D) and values (nkv * V);
 // bias and conv [channels, taps] in the same channel order (null: none; taps 0: no convolution); state [slots, taps - 1, channels]
-// float; cos_sin [positions, rotary / 2, 2] float (null: no rotation; pairs i, i + rotary / 2).
+// float; cos_sin [positions, rotary / 2, 2] float (null: no rotation; pairs i, i + rotary / 2). head_norm: the norm weights are
+// [D] and every head is normed by itself.
 extern "C" int ti_conv_attention_inputs(const void* proj, long long ld, const void* bias, const void* conv, int taps, const float* state,
                                         const void* q_norm_w, const void* k_norm_w, float eps, const float* cos_sin, int rotary, void* q_out,
                                         void* k_cache, void* v_cache, const int* positions, const int* slot_map, const int* cu_seqlens,
                                         const int* seq_slots, const int* kv_lens, int n, int B, int nq, int nkv, int D, int V, int Dp,
-                                        int page_size, int write_kv, int dtype, cudaStream_t stream) {
+                                        int page_size, int write_kv, int head_norm, int dtype, cudaStream_t stream) {
     if (n == 0) return 0;
     TI_REQUIRE(taps >= 0 && taps <= CI_MAX_TAPS && (taps <= 1 || state != nullptr) && (taps == 0 || conv != nullptr), "conv_attention_inputs: %d taps", taps);
     TI_REQUIRE(D > 0 && V > 0 && Dp >= D && Dp >= V && nq > 0 && nkv > 0, "conv_attention_inputs: heads of %d / %d in rows of %d", D, V, Dp);
@@ -138,7 +156,7 @@ extern "C" int ti_conv_attention_inputs(const void* proj, long long ld, const vo
         if (smem > 48 * 1024) cudaFuncSetAttribute(conv_attention_inputs_kernel<T, TAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         ti_launch(conv_attention_inputs_kernel<T, TAPS>, dim3(n), dim3(CI_THREADS), smem, stream, (const T*)proj, ld, (const T*)bias, (const T*)conv,  \
                   taps, state, (const T*)q_norm_w, (const T*)k_norm_w, eps, cos_sin, rotary, (T*)q_out, (T*)k_cache, (T*)v_cache, positions,       \
-                  slot_map, cu_seqlens, seq_slots, kv_lens, B, nq, nkv, D, V, Dp, page_size, write_kv);                                          \
+                  slot_map, cu_seqlens, seq_slots, kv_lens, B, nq, nkv, D, V, Dp, page_size, write_kv, head_norm);                               \
     } while (0)
     TI_DISPATCH_DTYPE(dtype, {
         switch (taps) {

@@ -355,7 +355,7 @@ extern "C" int ti_gemm_plain(void* y, long long ldy, const void* x, long long ld
                              cudaStream_t stream) {
     if (n == 0) return 0;
     TI_REQUIRE(n > 0 && out > 0 && in > 0, "gemm: bad sizes n=%d out=%d in=%d", n, out, in);
-    TI_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == TI_EPI_GELU_ERF || epilogue == TI_EPI_GELU_TANH, "gemm: unknown epilogue %d", epilogue);
+    TI_REQUIRE((epilogue >= 0 && epilogue <= 2) || (epilogue >= TI_EPI_GELU_ERF && epilogue <= TI_EPI_LAST), "gemm: unknown epilogue %d", epilogue);
     dim3 grid((out + GP_BN - 1) / GP_BN, (n + GP_BM - 1) / GP_BM);
     TI_REQUIRE(grid.y <= 65535, "gemm: too many rows (%d) for one launch", n);
     XieluParams act{alpha_p, alpha_n, beta, eps};

@@ -722,7 +722,7 @@ extern "C" int ti_gemm_tcgen05(void* y, long long ldy, const void* x, long long 
         ti_fail("gemm_tcgen05 needs 16-byte aligned rows: in=%d, ldx=%lld", in, ldx);
         return 2;
     }
-    TI_REQUIRE(epilogue >= 0 && epilogue <= TI_EPI_GELU_TANH, "gemm_tcgen05: unknown epilogue %d", epilogue);
+    TI_REQUIRE(epilogue >= 0 && epilogue <= TI_EPI_LAST, "gemm_tcgen05: unknown epilogue %d", epilogue);
     TI_REQUIRE(status != nullptr, "gemm_tcgen05: status word missing");
     static int sm_count = 0;
     if (!sm_count) {

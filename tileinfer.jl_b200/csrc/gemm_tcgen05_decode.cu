@@ -344,7 +344,7 @@ extern "C" int ti_gemm_tcgen05_decode(void* y, long long ldy, const void* x, lon
         ti_fail("gemm_tcgen05_decode takes up to %d tokens and 16-byte aligned rows: n=%d, in=%d, ldx=%lld", 2 * BMT, n, in, ldx);
         return 2;
     }
-    TI_REQUIRE(epilogue >= 0 && epilogue <= TI_EPI_GELU_TANH, "gemm_tcgen05_decode: unknown epilogue %d", epilogue);
+    TI_REQUIRE(epilogue >= 0 && epilogue <= TI_EPI_LAST, "gemm_tcgen05_decode: unknown epilogue %d", epilogue);
     TI_REQUIRE(status != nullptr, "gemm_tcgen05_decode: status word missing");
     const int sm_count = device_sm_count();
     if (nt <= 0) plan(n, out, in, 1, sm_count, &nt, &splits);

@@ -141,7 +141,7 @@ extern "C" int ti_gemv_bf16(void* y, long long ldy, const void* x, long long ldx
     TI_REQUIRE(in % 8 == 0 && ldx % 8 == 0, "gemv: in=%d and the row stride of x (%lld) must be multiples of 8", in, ldx);
     TI_REQUIRE(((uintptr_t)W % 16 == 0) && ((uintptr_t)x % 16 == 0), "gemv: operands must be 16-byte aligned");
     TI_REQUIRE(splits >= 1 && (splits == 1 || epilogue == GV_EPI_PARTIAL), "gemv: a split product leaves partial sums");
-    TI_REQUIRE(epilogue >= 0 && epilogue <= TI_EPI_GELU_TANH, "gemv: unknown epilogue %d", epilogue);
+    TI_REQUIRE(epilogue >= 0 && epilogue <= TI_EPI_LAST, "gemv: unknown epilogue %d", epilogue);
     dim3 grid((out + 15) / 16, splits);
     XieluParams act{alpha_p, alpha_n, beta, eps};
     if (n <= 8)

@@ -1,12 +1,15 @@
 // A residual stream kept in 32-bit, whatever the element type T of the activations and weights is.
 //
 //   embed_positions32   x = E[id] + P[position]                                  (both tables in T, the sum in 32-bit)
-//   cast_rows           h = T(x)
+//   embed_bigram32      x = E[id] * scale + G[(previous id * a + id * b) mod buckets]   (the row `buckets` for a sequence's first token)
+//   cast_rows           h = T(x)                                                    (h's rows may be longer than x's)
 //   norm32              y = T(x / rms(x) * g(w)),  x in 32-bit or in T
 //   branch_norm_add32   x += mult * d / rms(d) * g(w);  then  h = T(x)  or  h = T(x / rms(x) * g_out(w_out))
 //   sum_add_norm32      x += d1 + d2;  then  h = T(x / rms(x) * g_out(w_out))       (two sublayers that read the same input)
 //
-// rms(v) = sqrt(mean(v^2) + eps); g(w) = w, or 1 + w where the checkpoint keeps the gain minus one ("offset"). Everything
+// rms(v) = sqrt(mean(v^2) + eps); g(w) = w, or 1 + w where the checkpoint keeps the gain minus one ("offset"). A norm's flags
+// word carries that choice in bit 0 and, in bit 1, "centred": the row's mean is taken off first and rms is then the root of the
+// mean squared deviation (a layer norm with a weight and no bias). branch_norm_add32 may add a bias vector to d first. Everything
 // between the loads and the one rounding on store is 32-bit. d is a sublayer's output: [n, size] in T, or the
 // 32-bit partial sums [s, n, size] of a product that was cut over k (added in split order, not rounded).
 // One block per row; the order of a row's sums depends on the row's size alone.
@@ -46,6 +49,89 @@ extern "C" int ti_embed_positions32(float* x, const void* table, const void* pos
     return ti_check_launch("embed_positions32");
 }
 
+// A token embedding times a constant plus a row of a second table chosen by a hash of the token and the token before it in
+// its sequence. The token before comes from the step itself, or, where the step begins in the middle of a sequence, from `last`
+// [slots]: the last token that earlier steps ran, which last_token_update writes after this kernel (a launch of its own,
+// since these blocks read what it overwrites). A sequence's first token takes the table's extra row `buckets`. pair == null: no
+// second table.
+template <typename T>
+__global__ void embed_bigram32_kernel(float* __restrict__ x, const T* __restrict__ table, const T* __restrict__ pair, const int* ids,
+                                      const int* positions, const int* tok_slot, const int* last, int hidden, int vocab, float scale,
+                                      long long buckets, long long mul_prev, long long mul_cur, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    pdl_enter();
+    int id = __ldcg(ids + t);
+    const int p = __ldcg(positions + t);
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicExch(status, 1 + t);
+        id = 0;
+    }
+    const T* g = nullptr;
+    if (pair != nullptr) {
+        long long row = buckets;
+        if (p > 0) {
+            const int slot = __ldcg(tok_slot + t);
+            int prev;
+            if (t > 0 && __ldcg(tok_slot + t - 1) == slot && __ldcg(positions + t - 1) == p - 1) prev = __ldcg(ids + t - 1);
+            else prev = __ldcg(last + slot);
+            if (prev < 0 || prev >= vocab) prev = 0;
+            row = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+            if (row < 0) row += buckets;
+        }
+        g = pair + (size_t)row * hidden;
+    }
+    const T* e = table + (size_t)id * hidden;
+    float* dst = x + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = to_f32(e[i]) * scale;
+        dst[i] = g != nullptr ? v + to_f32(g[i]) : v;
+    }
+}
+
+extern "C" int ti_embed_bigram32(float* x, const void* table, const void* pair, const int* ids, const int* positions, const int* tok_slot,
+                                 const int* last, int n_tokens, int hidden, int vocab, float scale, long long buckets, long long mul_prev,
+                                 long long mul_cur, int dtype, int* status, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    TI_REQUIRE(hidden > 0 && vocab > 0 && (pair == nullptr || (buckets > 0 && last != nullptr)), "embed_bigram32: hidden %d vocab %d buckets %lld",
+               hidden, vocab, buckets);
+    const int threads = hidden >= 1024 ? 256 : 128;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(embed_bigram32_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, x, (const T*)table, (const T*)pair, ids,
+                                        positions, tok_slot, last, hidden, vocab, scale, buckets, mul_prev, mul_cur, status)));
+    return ti_check_launch("embed_bigram32");
+}
+
+__global__ void last_token_update_kernel(int* last, const int* ids, const int* cu_seqlens, const int* seq_slots, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_enter();
+    if (b < B) last[__ldcg(seq_slots + b)] = __ldcg(ids + __ldcg(cu_seqlens + b + 1) - 1);
+}
+
+extern "C" int ti_last_token_update(int* last, const int* ids, const int* cu_seqlens, const int* seq_slots, int B, cudaStream_t stream) {
+    if (B == 0) return 0;
+    ti_launch(last_token_update_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, last, ids, cu_seqlens, seq_slots, B);
+    return ti_check_launch("last_token_update");
+}
+
+// h [n, ldh] (the first `size` elements of every row) = T(x [n, size]).
+template <typename T>
+__global__ void cast_rows_ld_kernel(T* __restrict__ h, long long ldh, const float* x, int size, size_t count) {
+    pdl_enter();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / size;
+        h[t * ldh + (i - t * size)] = from_f32<T>(__ldcg(x + i));
+    }
+}
+
+extern "C" int ti_cast_rows_ld(void* h, long long ldh, const float* x, int n, int size, int dtype, cudaStream_t stream) {
+    const long long count = (long long)n * size;
+    if (count == 0) return 0;
+    TI_REQUIRE(ldh >= size, "cast_rows_ld: rows of %d in a buffer with rows of %lld", size, ldh);
+    long long blocks = (count + 255) / 256;
+    if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(cast_rows_ld_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)h, ldh, x, size, (size_t)count)));
+    return ti_check_launch("cast_rows_ld");
+}
+
 template <typename T>
 __global__ void cast_rows_kernel(T* __restrict__ h, const float* x, size_t count) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -70,17 +156,22 @@ __global__ void norm32_kernel(T* __restrict__ y, const X* x, const T* __restrict
     __shared__ float scratch[33];
     const X* row = x + (size_t)blockIdx.x * size;
     T* dst = y + (size_t)blockIdx.x * size;
-    float ss = 0.f;
+    float ss = 0.f, mean = 0.f;
     pdl_enter();
+    if (offset & 2) {
+        float s = 0.f;
+        for (int i = threadIdx.x; i < size; i += blockDim.x) s += to_f32(__ldcg(row + i));
+        mean = block_sum(s, scratch) / (float)size;
+    }
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
-        const float v = to_f32(__ldcg(row + i));
+        const float v = to_f32(__ldcg(row + i)) - mean;
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)size + eps);
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
-        const float g = offset ? 1.0f + to_f32(w[i]) : to_f32(w[i]);
-        dst[i] = from_f32<T>(to_f32(__ldcg(row + i)) * inv * g);
+        const float g = (offset & 1) ? 1.0f + to_f32(w[i]) : to_f32(w[i]);
+        dst[i] = from_f32<T>((to_f32(__ldcg(row + i)) - mean) * inv * g);
     }
 }
 
@@ -100,12 +191,12 @@ extern "C" int ti_norm32(void* y, const void* x, int x_is_f32, const void* w, in
 // `delta` (the outputs of the units a token went through), instead of row `row` of `delta`.
 template <typename T>
 __global__ void branch_norm_add32_kernel(float* x, const T* delta, const float* partials, int n_partials, size_t partial_stride,
-                                         const int* gather, int per_row, const T* __restrict__ w, int offset, float eps, float mult, T* __restrict__ h,
-                                         const T* __restrict__ w_out, int offset_out, float eps_out, int size) {
+                                         const int* gather, int per_row, const T* __restrict__ dbias, const T* __restrict__ w, int offset, float eps,
+                                         float mult, T* __restrict__ h, const T* __restrict__ w_out, int offset_out, float eps_out, int size) {
     extern __shared__ float row_d[];           // [size]: the branch's row, then the stream's new row
     __shared__ float scratch[33];
     float* row = x + (size_t)blockIdx.x * size;
-    float ss = 0.f;
+    float ss = 0.f, sum = 0.f;
     pdl_enter();
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
         float d;
@@ -120,18 +211,30 @@ __global__ void branch_norm_add32_kernel(float* x, const T* delta, const float* 
         } else {
             d = to_f32(__ldcg(delta + (size_t)blockIdx.x * size + i));
         }
+        if (dbias != nullptr) d += to_f32(dbias[i]);
         row_d[i] = d;
         ss = fmaf(d, d, ss);
+        sum += d;
+    }
+    float mean = 0.f;
+    if (offset & 2) {                          // centred: the squared deviations need the mean first (a thread reads back its own elements)
+        mean = block_sum(sum, scratch) / (float)size;
+        ss = 0.f;
+        for (int i = threadIdx.x; i < size; i += blockDim.x) {
+            const float d = row_d[i] - mean;
+            ss = fmaf(d, d, ss);
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)size + eps);
-    float ss2 = 0.f;
+    float ss2 = 0.f, sum2 = 0.f;
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
-        const float g = offset ? 1.0f + to_f32(w[i]) : to_f32(w[i]);
-        const float v = __ldcg(row + i) + mult * (row_d[i] * inv * g);
+        const float g = (offset & 1) ? 1.0f + to_f32(w[i]) : to_f32(w[i]);
+        const float v = __ldcg(row + i) + mult * ((row_d[i] - mean) * inv * g);
         row[i] = v;
         row_d[i] = v;                         // the same thread reads it back below
         ss2 = fmaf(v, v, ss2);
+        sum2 += v;
     }
     if (h == nullptr) return;
     T* dst = h + (size_t)blockIdx.x * size;
@@ -139,11 +242,20 @@ __global__ void branch_norm_add32_kernel(float* x, const T* delta, const float* 
         for (int i = threadIdx.x; i < size; i += blockDim.x) dst[i] = from_f32<T>(row_d[i]);
         return;
     }
+    float mean2 = 0.f;
+    if (offset_out & 2) {
+        mean2 = block_sum(sum2, scratch) / (float)size;
+        ss2 = 0.f;
+        for (int i = threadIdx.x; i < size; i += blockDim.x) {
+            const float d = row_d[i] - mean2;
+            ss2 = fmaf(d, d, ss2);
+        }
+    }
     ss2 = block_sum(ss2, scratch);
     const float inv2 = 1.0f / sqrtf(ss2 / (float)size + eps_out);
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
-        const float g = offset_out ? 1.0f + to_f32(w_out[i]) : to_f32(w_out[i]);
-        dst[i] = from_f32<T>(row_d[i] * inv2 * g);
+        const float g = (offset_out & 1) ? 1.0f + to_f32(w_out[i]) : to_f32(w_out[i]);
+        dst[i] = from_f32<T>((row_d[i] - mean2) * inv2 * g);
     }
 }
 
@@ -165,12 +277,13 @@ __device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
 }
 
 __global__ void branch_norm_add32_vec_kernel(float* x, const bf16* delta, const float* partials, int n_partials, size_t partial_stride,
-                                             const int* gather, int per_row, const bf16* __restrict__ w, int offset, float eps, float mult,
-                                             bf16* __restrict__ h, const bf16* __restrict__ w_out, int offset_out, float eps_out, int size) {
+                                             const int* gather, int per_row, const bf16* __restrict__ dbias, const bf16* __restrict__ w, int offset,
+                                             float eps, float mult, bf16* __restrict__ h, const bf16* __restrict__ w_out, int offset_out, float eps_out,
+                                             int size) {
     extern __shared__ float row_d[];
     __shared__ float scratch[33];
     float* row = x + (size_t)blockIdx.x * size;
-    float ss = 0.f;
+    float ss = 0.f, sum = 0.f;
     pdl_enter();
     for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
         float d[4];
@@ -192,13 +305,33 @@ __global__ void branch_norm_add32_vec_kernel(float* x, const bf16* delta, const 
         } else {
             load4(delta + (size_t)blockIdx.x * size + i, d);
         }
+        if (dbias != nullptr) {
+            float b[4];
+            load4w(dbias + i, b);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) d[e] += b[e];
+        }
         *reinterpret_cast<float4*>(row_d + i) = make_float4(d[0], d[1], d[2], d[3]);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) ss = fmaf(d[e], d[e], ss);
+        for (int e = 0; e < 4; ++e) {
+            ss = fmaf(d[e], d[e], ss);
+            sum += d[e];
+        }
+    }
+    float mean = 0.f;
+    if (offset & 2) {
+        mean = block_sum(sum, scratch) / (float)size;
+        ss = 0.f;
+        for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+            const float4 t = *reinterpret_cast<const float4*>(row_d + i);
+            const float d[4] = {t.x - mean, t.y - mean, t.z - mean, t.w - mean};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss = fmaf(d[e], d[e], ss);
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)size + eps);
-    float ss2 = 0.f;
+    float ss2 = 0.f, sum2 = 0.f;
     for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
         float g[4];
         load4w(w + i, g);
@@ -208,16 +341,27 @@ __global__ void branch_norm_add32_vec_kernel(float* x, const bf16* delta, const 
         float v[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            v[e] = xs[e] + mult * (ds[e] * inv * (offset ? 1.0f + g[e] : g[e]));
+            v[e] = xs[e] + mult * ((ds[e] - mean) * inv * ((offset & 1) ? 1.0f + g[e] : g[e]));
             ss2 = fmaf(v[e], v[e], ss2);
+            sum2 += v[e];
         }
         *reinterpret_cast<float4*>(row + i) = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4*>(row_d + i) = make_float4(v[0], v[1], v[2], v[3]);
     }
     if (h == nullptr) return;
     bf16* dst = h + (size_t)blockIdx.x * size;
-    float inv2 = 1.0f;
+    float inv2 = 1.0f, mean2 = 0.f;
     if (w_out != nullptr) {
+        if (offset_out & 2) {
+            mean2 = block_sum(sum2, scratch) / (float)size;
+            ss2 = 0.f;
+            for (int i = threadIdx.x * 4; i < size; i += blockDim.x * 4) {
+                const float4 t = *reinterpret_cast<const float4*>(row_d + i);
+                const float d[4] = {t.x - mean2, t.y - mean2, t.z - mean2, t.w - mean2};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ss2 = fmaf(d[e], d[e], ss2);
+            }
+        }
         ss2 = block_sum(ss2, scratch);
         inv2 = 1.0f / sqrtf(ss2 / (float)size + eps_out);
     }
@@ -228,15 +372,15 @@ __global__ void branch_norm_add32_vec_kernel(float* x, const bf16* delta, const 
             float g[4];
             load4w(w_out + i, g);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) v[e] = v[e] * inv2 * (offset_out ? 1.0f + g[e] : g[e]);
+            for (int e = 0; e < 4; ++e) v[e] = (v[e] - mean2) * inv2 * ((offset_out & 1) ? 1.0f + g[e] : g[e]);
         }
         store4(dst + i, v);
     }
 }
 
 extern "C" int ti_branch_norm_add32(float* x, const void* delta, const float* partials, int n_partials, long long partial_stride,
-                                    const int* gather, int per_row, const void* w, int offset, float eps, float mult, void* h, const void* w_out, int offset_out,
-                                    float eps_out, int n_rows, int size, int dtype, cudaStream_t stream) {
+                                    const int* gather, int per_row, const void* dbias, const void* w, int offset, float eps, float mult, void* h,
+                                    const void* w_out, int offset_out, float eps_out, int n_rows, int size, int dtype, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     TI_REQUIRE(size > 0 && size <= 50000, "branch_norm_add32: size %d", size);
     TI_REQUIRE((delta != nullptr) != (partials != nullptr), "branch_norm_add32: give delta or partials, not both");
@@ -253,14 +397,16 @@ extern "C" int ti_branch_norm_add32(float* x, const void* delta, const float* pa
             }
         }
         const bool vec = sizeof(T) == 2 && size % 4 == 0 && smem <= 48 * 1024 && aligned16(x) && (partials == nullptr || (aligned16(partials) && partial_stride % 4 == 0)) &&
-                         (((uintptr_t)delta | (uintptr_t)w | (uintptr_t)h | (uintptr_t)w_out) & 7) == 0;
+                         (((uintptr_t)delta | (uintptr_t)dbias | (uintptr_t)w | (uintptr_t)h | (uintptr_t)w_out) & 7) == 0;
         if (vec) {
             const int vt = size >= 2048 ? 256 : 128;
             ti_launch(branch_norm_add32_vec_kernel, dim3(n_rows), dim3(vt), smem, stream, x, (const bf16*)delta, partials, n_partials,
-                      (size_t)partial_stride, gather, per_row, (const bf16*)w, offset, eps, mult, (bf16*)h, (const bf16*)w_out, offset_out, eps_out, size);
+                      (size_t)partial_stride, gather, per_row, (const bf16*)dbias, (const bf16*)w, offset, eps, mult, (bf16*)h, (const bf16*)w_out,
+                      offset_out, eps_out, size);
         } else
         ti_launch(branch_norm_add32_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, x, (const T*)delta, partials, n_partials,
-                  (size_t)partial_stride, gather, per_row, (const T*)w, offset, eps, mult, (T*)h, (const T*)w_out, offset_out, eps_out, size);
+                  (size_t)partial_stride, gather, per_row, (const T*)dbias, (const T*)w, offset, eps, mult, (T*)h, (const T*)w_out, offset_out, eps_out,
+                  size);
     });
     return ti_check_launch("branch_norm_add32");
 }

@@ -22,8 +22,13 @@ def tensor_declarations(spec: ModelSpec) -> List[TensorDecl]:
     """Every checkpoint tensor a model of this spec reads."""
     decls = list(lookup("embedding", spec.embedding_kind).tensors(spec)) + list(lookup("head", spec.head_kind).tensors(spec))
     decls += lookup("norm", spec.final_norm.kind).tensors(spec.final_norm)
+    if spec.pass_input is not None:
+        decls += lookup("pass_input", spec.pass_input.kind).tensors(spec.pass_input)
     for layer in spec.layers:
         decls += lookup("norm", layer.mixer_norm.kind).tensors(layer.mixer_norm)
+        for post in (layer.mixer_post_norm, layer.feed_forward_post_norm):
+            if post is not None:
+                decls += lookup("norm", post.kind).tensors(post)
         decls += lookup("mixer", layer.mixer.kind).tensors(layer.mixer)
         if layer.feed_forward is not None:
             if layer.feed_forward_norm is not None:          # an arrangement with one norm for both sublayers has none
@@ -50,6 +55,10 @@ class DecoderModel:
         self.max_positions = int(min(max_positions, spec.max_positions))
         self.embedding = lookup("embedding", spec.embedding_kind)(spec, tensors, rt)
         self.head = lookup("head", spec.head_kind)(spec, tensors, rt, self.embedding)
+        # An embedding that keeps something per sequence (the token before, for one) has the cache entry after the layer runs'.
+        ask = getattr(self.embedding, "cache_request", None)
+        self._embedding_request = ask() if ask is not None else None
+        self._embedding_cache = len(spec.order) if self._embedding_request is not None else None
         self.final_norm = lookup("norm", spec.final_norm.kind)(spec.final_norm, tensors, rt)
         self._positions: Dict[tuple, object] = {}
         self.blocks = []
@@ -65,7 +74,19 @@ class DecoderModel:
             extra = {}
             if layer.token_input is not None:
                 extra["token_input"] = lookup("token_input", layer.token_input.kind)(layer.token_input, tensors, rt)
+            if layer.mixer_post_norm is not None:
+                extra["mixer_post_norm"] = lookup("norm", layer.mixer_post_norm.kind)(layer.mixer_post_norm, tensors, rt)
+            if layer.feed_forward_post_norm is not None:
+                extra["feed_forward_post_norm"] = lookup("norm", layer.feed_forward_post_norm.kind)(layer.feed_forward_post_norm, tensors, rt)
             self.blocks.append(lookup("block", layer.block)(layer, mixer, ffn, n1, n2, **extra))
+        self.pass_input = None
+        if spec.pass_input is not None:
+            self.pass_input = lookup("pass_input", spec.pass_input.kind)(spec.pass_input, tensors, rt)
+            if any(not 0 <= occ < len(spec.order) for occ in spec.pass_input.at):
+                raise ValueError(f"pass input before layer runs {spec.pass_input.at} of {len(spec.order)}")
+        self._pass_starts = frozenset(spec.pass_input.at) if spec.pass_input is not None else frozenset()
+        # Called with (index of the layer run, the 32-bit or 16-bit stream after it) when set: for tests and debugging.
+        self.observer = None
         self.status = torch.zeros(1, dtype=torch.int32, device=rt.device)
         # The residual stream has the products' element type unless the architecture keeps it in 32-bit.
         self.stream_dtype = torch.float32 if spec.options.get("residual_dtype") == "float32" else rt.dtype
@@ -78,7 +99,11 @@ class DecoderModel:
 
     # ---- what the cache has to hold, one entry per position of ``order``
     def cache_requests(self):
-        return [self.blocks[li].mixer.cache_request() for li in self.spec.order]
+        """One entry per layer run; then one for the embedding, if it keeps something per sequence."""
+        out = [self.blocks[li].mixer.cache_request() for li in self.spec.order]
+        if self._embedding_request is not None:
+            out.append(self._embedding_request)
+        return out
 
     def cache_shares(self) -> Dict[int, int]:
         """occurrence -> the earlier occurrence whose storage it reads."""
@@ -118,8 +143,9 @@ class DecoderModel:
                     visit(v)
 
         for b in self.blocks:
-            visit([b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm, getattr(b, "token_input", None)])
-        visit([self.final_norm, self.head])
+            visit([b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm, getattr(b, "token_input", None),
+                   getattr(b, "mixer_post_norm", None), getattr(b, "feed_forward_post_norm", None)])
+        visit([self.final_norm, self.head, self.pass_input])
         return total
 
     def forward(self, step, cache, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -134,15 +160,25 @@ class DecoderModel:
         x = rt.buffer("model.x", (n, spec.hidden_size), self.stream_dtype)
         h = rt.buffer("model.h", (n, spec.hidden_size))
         embed_step = getattr(self.embedding, "forward_step", None)
-        if embed_step is not None:
+        if self._embedding_cache is not None:
+            embed_step(step, x, self.status, cache=cache.layer(self._embedding_cache))
+        elif embed_step is not None:
             embed_step(step, x, self.status)
         else:
             self.embedding.forward(step.token_ids, x, self.status)
+        if self.pass_input is not None:
+            self.pass_input.begin(x)
         order = spec.order
         self.blocks[order[0]].input_norm.forward(x, h) if order else self.final_norm.forward(x, h)
         for occ, li in enumerate(order):
+            if occ in self._pass_starts:
+                # The stream is rewritten before this run; the normed input that the run before left is made again.
+                self.pass_input.forward(x)
+                self.blocks[li].input_norm.forward(x, h)
             nxt = self.blocks[order[occ + 1]].input_norm if occ + 1 < len(order) else self.final_norm
             self.blocks[li].forward(x, h, step, cache.layer(occ), nxt, h)
+            if self.observer is not None:
+                self.observer(occ, x)
         if logits is None or step.n_want == 0:
             return None
         hw = rt.buffer("model.h_wanted", (step.n_want, spec.hidden_size))

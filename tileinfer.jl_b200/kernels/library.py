@@ -166,8 +166,8 @@ _SIGNATURES.update({
     "ti_embed_positions32": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "ti_cast_rows": [_P, _P, _L, _I, _P],
     "ti_norm32": [_P, _P, _I, _P, _I, _I, _F, _I, _I, _P],
-    "ti_branch_norm_add32": [_P, _P, _P, _I, _L, _P, _I, _P, _I, _F, _F, _P, _P, _I, _F, _I, _I, _I, _P],
-    "ti_latent_inputs": [_P, _L, _P, _I, _L, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _P],
+    "ti_branch_norm_add32": [_P, _P, _P, _I, _L, _P, _I, _P, _P, _I, _F, _F, _P, _P, _I, _F, _I, _I, _I, _P],
+    "ti_latent_inputs": [_P, _L, _P, _I, _L, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _P, _I, _P, _I, _L, _I, _P],
     "ti_head_gemm": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _P],
     "ti_gelu": [_P, _P, _L, _I, _I, _P],
     "ti_gated_token_embedding": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -187,10 +187,19 @@ _SIGNATURES.update({
     "ti_lightning_scan": [_P, _P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_lightning_out": [_P, _P, _P, _L, _P, _F, _I, _I, _I, _P],
     "ti_conv_attention_inputs": [_P, _L, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                                 _I, _P],
+                                 _I, _I, _P],
     "ti_conv_state_update": [_P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _P],
     "ti_sigmoid_gate": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
     "ti_sum_add_norm32": [_P, _P, _P, _I, _L, _P, _P, _I, _L, _P, _P, _I, _F, _I, _I, _I, _P],
     "ti_router_select": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P],
     "ti_gated_act": [_P, _P, _I, _I, _I, _I, _P],
+})
+
+# A scaled embedding plus a row chosen by a hash of two consecutive tokens, rows cast into a wider buffer, a rotation of a part of
+# every head in place.
+_SIGNATURES.update({
+    "ti_embed_bigram32": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _L, _L, _L, _I, _P, _P],
+    "ti_last_token_update": [_P, _P, _P, _P, _I, _P],
+    "ti_cast_rows_ld": [_P, _L, _P, _I, _I, _I, _P],
+    "ti_rotate_heads": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
 })

@@ -17,6 +17,7 @@ from .library import KernelError, check, lib
 F32, BF16 = 0, 1
 EPI_NONE, EPI_XIELU, EPI_F32_OUT = 0, 1, 2
 EPI_GELU_ERF, EPI_GELU_TANH = 4, 5          # GELU of the rounded sum, exact or tanh form (3: raw partial sums, inside the library)
+EPI_RELU2 = 6                               # max(rounded sum, 0)^2
 MAX_HEAD_DIM = 512      # the largest head the attention kernels take (csrc/attention_inputs.cu, csrc/attention_plain.cu)
 
 
@@ -214,25 +215,79 @@ def embed_positions32(x, table, pos_table, ids, positions, status):
           "embed_positions32")
 
 
+def embed_bigram32(x, table, pair, ids, positions, tok_slot, last, scale, buckets=0, mul_prev=0, mul_cur=0, status=None):
+    """x[t] = table[ids[t]] * scale + pair[(previous id * mul_prev + ids[t] * mul_cur) mod buckets] in 32-bit; the token before comes
+    from the step or, at the step's start, from ``last`` [slots] int32; a sequence's first token takes row ``buckets`` of ``pair``
+    [buckets + 1, hidden]. ``pair`` None: the scaled row alone."""
+    _need(x, "x", torch.float32); _need(table, "table"); _need(ids, "ids", torch.int32); _need(positions, "positions", torch.int32)
+    _need(tok_slot, "tok_slot", torch.int32); _need(status, "status", torch.int32)
+    n, hidden = x.shape
+    if pair is not None:
+        _need(pair, "pair", table.dtype); _need(last, "last", torch.int32)
+        if tuple(pair.shape) != (buckets + 1, hidden):
+            raise KernelError(f"embed_bigram32: second table {tuple(pair.shape)} for {buckets} buckets and a width of {hidden}")
+    if table.shape[1] != hidden:
+        raise KernelError(f"embed_bigram32: table {tuple(table.shape)} for a width of {hidden}")
+    check(lib().ti_embed_bigram32(x.data_ptr(), table.data_ptr(), _ptr(pair), ids.data_ptr(), positions.data_ptr(), tok_slot.data_ptr(), _ptr(last), n,
+                                  hidden, table.shape[0], scale, buckets, mul_prev, mul_cur, dtype_code(table.dtype), status.data_ptr(), _stream()),
+          "embed_bigram32")
+
+
+def last_token_update(last, step):
+    """last[slot] = the last token that the step brings for the sequence in ``slot``."""
+    _need(last, "last", torch.int32)
+    check(lib().ti_last_token_update(last.data_ptr(), step.token_ids.data_ptr(), step.cu_seqlens.data_ptr(), step.seq_slots.data_ptr(), step.n_seqs,
+                                     _stream()), "last_token_update")
+
+
+def cast_rows_into(h, x):
+    """h[:, :size] = x rounded to h's element type for h a view [n, size] of rows that may be longer (stride(0) >= size); x is 32-bit."""
+    _need(h, "h", contiguous=False); _need(x, "x", torch.float32)
+    if h.stride(1) != 1 or h.shape != x.shape:
+        raise KernelError(f"cast_rows_into: h {tuple(h.shape)} with strides {h.stride()} for x {tuple(x.shape)}")
+    check(lib().ti_cast_rows_ld(h.data_ptr(), h.stride(0), x.data_ptr(), x.shape[0], x.shape[1], dtype_code(h.dtype), _stream()), "cast_rows_into")
+
+
+def rotate_heads(x, rotation, positions, first=0):
+    """x [n, heads, row]: the elements [first, first + rotary_dim) of every head are rotated in place by the positions' angles."""
+    _need(x, "x"); _need(positions, "positions", torch.int32); _need(rotation.cos_sin, "cos_sin", torch.float32)
+    n, heads, row = x.shape
+    rot = int(rotation.rotary_dim)
+    if rotation.cos_sin.shape[1] * 2 != rot:
+        raise KernelError(f"rotate_heads: {rot} elements with a table of {tuple(rotation.cos_sin.shape)}")
+    check(lib().ti_rotate_heads(x.data_ptr(), rotation.cos_sin.data_ptr(), positions.data_ptr(), n, heads, row, first, rot,
+                                int(bool(rotation.interleaved)), dtype_code(x.dtype), _stream()), "rotate_heads")
+
+
 def cast_rows(h, x):
     """h = x rounded to h's element type; x is 32-bit."""
     _need(h, "h"); _need(x, "x", torch.float32)
     check(lib().ti_cast_rows(h.data_ptr(), x.data_ptr(), x.numel(), dtype_code(h.dtype), _stream()), "cast_rows")
 
 
+NORM_OFFSET, NORM_CENTRED = 1, 2          # bits of a norm's flags word: the gain is 1 + w; the row's mean is taken off first
+
+
+def norm_flags(offset) -> int:
+    """``offset`` as the wrappers take it: a bool (the gain is 1 + w) or the flags word itself."""
+    return int(offset) if isinstance(offset, int) and not isinstance(offset, bool) else int(bool(offset))
+
+
 def norm32(y, x, w, eps, offset=False):
-    """y = x / rms(x) * (1 + w if offset else w), computed in 32-bit; x is 32-bit or of y's type."""
+    """y = x / rms(x) * (1 + w if offset else w), computed in 32-bit; x is 32-bit or of y's type. ``offset`` may be a flags
+    word: with NORM_CENTRED the row's mean is taken off and rms is that of the deviations."""
     _need(y, "y"); _need(x, "x"); _need(w, "w", y.dtype)
     if x.dtype not in (torch.float32, y.dtype):
         raise KernelError(f"norm32: input must be float32 or {y.dtype}")
     size = x.shape[-1]
     check(lib().ti_norm32(y.data_ptr(), x.data_ptr(), int(x.dtype == torch.float32), w.data_ptr(), x.numel() // size, size, eps,
-                          int(bool(offset)), dtype_code(y.dtype), _stream()), "norm32")
+                          norm_flags(offset), dtype_code(y.dtype), _stream()), "norm32")
 
 
-def branch_norm_add32(x, delta, w, eps, mult, offset=False, h=None, out_norm=None, gather=None):
+def branch_norm_add32(x, delta, w, eps, mult, offset=False, h=None, out_norm=None, gather=None, bias=None):
     """x += mult * delta / rms(delta) * g(w) in 32-bit (``delta``: [n, size] of w's type, or 32-bit partial sums
     [s, n, size]); then, with ``h``, h = x rounded, or h = x / rms(x) * g(w_out) for ``out_norm`` = (w_out, eps, offset).
+    ``bias`` [size]: added to delta before its norm. ``offset`` (both) may be a flags word (NORM_CENTRED: a layer norm).
     ``gather`` [n, k] int32: row t of the branch is the sum of the rows gather[t, :] of ``delta`` [rows, size]."""
     _need(x, "x", torch.float32); _need(w, "w")
     n, size = x.shape
@@ -254,26 +309,38 @@ def branch_norm_add32(x, delta, w, eps, mult, offset=False, h=None, out_norm=Non
     w_out, eps_out, offset_out = out_norm if out_norm is not None else (None, 0.0, False)
     if w_out is not None:
         _need(w_out, "w_out", w.dtype)
-    check(lib().ti_branch_norm_add32(x.data_ptr(), *d_args, *g_args, w.data_ptr(), int(bool(offset)), eps, mult, _ptr(h), _ptr(w_out),
-                                     int(bool(offset_out)), eps_out, n, size, dtype_code(w.dtype), _stream()), "branch_norm_add32")
+    if bias is not None:
+        _need(bias, "bias", w.dtype)
+    check(lib().ti_branch_norm_add32(x.data_ptr(), *d_args, *g_args, _ptr(bias), w.data_ptr(), norm_flags(offset), eps, mult, _ptr(h), _ptr(w_out),
+                                     norm_flags(offset_out), eps_out, n, size, dtype_code(w.dtype), _stream()), "branch_norm_add32")
 
 
-def latent_inputs(rows, cq, pool, wq, wkv, eps, slots, q_rank, kv_rank):
-    """rows [n, q_rank + kv_rank] (or 32-bit partial sums [s, n, ...]) -> cq [n, q_rank] and the key/value latent of every
-    token at its place ``slots[t]`` of ``pool`` [positions, kv_rank]; both RMS-normed in 32-bit with plain weights."""
+def latent_inputs(rows, cq, pool, wq, wkv, eps, slots, q_rank, kv_rank, rotation=None, positions=None, pool_row=None):
+    """rows [n, >= q_rank + kv_rank] (or 32-bit partial sums [s, n, ...]) -> cq [n, q_rank] and the key/value latent of every
+    token at its place ``slots[t]`` of ``pool`` [positions, pool_row]; both RMS-normed in 32-bit with plain weights. With
+    ``rotation`` the rotary_dim elements after the latents are a key part shared by all heads: rotated by ``positions`` and
+    written behind the latent in the pool's row (``pool_row`` >= kv_rank + rotary_dim elements, zeros after)."""
+    rot = int(rotation.rotary_dim) if rotation is not None else 0
+    pool_row = int(pool_row or kv_rank)
+    if rotation is not None:
+        _need(rotation.cos_sin, "cos_sin", torch.float32); _need(positions, "positions", torch.int32)
+        if rotation.cos_sin.shape[1] * 2 != rot:
+            raise KernelError(f"latent_inputs: {rot} rotated elements with a table of {tuple(rotation.cos_sin.shape)}")
     _need(cq, "cq"); _need(pool, "pool", cq.dtype); _need(wq, "wq", cq.dtype); _need(wkv, "wkv", cq.dtype); _need(slots, "slots", torch.int32)
     if rows.dim() == 3:
         _need(rows, "partial sums", torch.float32)
         args = (None, 0, rows.data_ptr(), rows.shape[0], rows.stride(0))
-        n = rows.shape[1]
+        n, in_row = rows.shape[1], rows.shape[2]
     else:
         _need(rows, "rows", cq.dtype, contiguous=False)
         if rows.stride(1) != 1:
             raise KernelError("latent_inputs: rows must be dense")
         args = (rows.data_ptr(), rows.stride(0), None, 0, 0)
-        n = rows.shape[0]
+        n, in_row = rows.shape[0], rows.shape[1]
     check(lib().ti_latent_inputs(*args, cq.data_ptr(), pool.data_ptr(), wq.data_ptr(), wkv.data_ptr(), eps, slots.data_ptr(), n,
-                                 q_rank, kv_rank, dtype_code(cq.dtype), _stream()), "latent_inputs")
+                                 q_rank, kv_rank, rot, _ptr(rotation.cos_sin) if rotation is not None else None,
+                                 int(bool(rotation.interleaved)) if rotation is not None else 0, _ptr(positions), pool_row, in_row,
+                                 dtype_code(cq.dtype), _stream()), "latent_inputs")
 
 
 def head_gemm(y, x, w):
@@ -431,10 +498,11 @@ def lightning_out(y, o, gate, w, eps):
 
 
 def conv_attention_inputs(rows, bias, conv, taps, state, q_norm_w, k_norm_w, eps, rotation, q_out, k_cache, v_cache, step, slot_map,
-                          nq, nkv, dim, vdim, padded, page_size, write_kv=True):
+                          nq, nkv, dim, vdim, padded, page_size, write_kv=True, head_norm=False):
     """The step's projected rows (queries, then keys and values with ``write_kv``) -> bias, causal convolution over time (history
-    from ``state`` [slots, taps - 1, channels] float32), whole-row RMS norms of q and k, rotation -> q_out [n, nq, padded] and the
-    keys and values at ``slot_map`` in the pools. ``step`` gives positions, cu_seqlens, seq_slots, kv_lens."""
+    from ``state`` [slots, taps - 1, channels] float32), whole-row RMS norms of q and k (``head_norm``: every head by itself, with
+    one weight of the head's size), rotation -> q_out [n, nq, padded] and the keys and values at ``slot_map`` in the pools. ``step``
+    gives positions, cu_seqlens, seq_slots, kv_lens."""
     _need(rows, "rows", q_out.dtype, contiguous=False); _need(q_out, "q_out")
     cos_sin = rotation.cos_sin if rotation is not None else None
     rotary = int(rotation.rotary_dim) if rotation is not None else 0
@@ -446,7 +514,7 @@ def conv_attention_inputs(rows, bias, conv, taps, state, q_norm_w, k_norm_w, eps
                                          eps, _ptr(cos_sin), rotary, q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), step.positions.data_ptr(),
                                          _ptr(slot_map), step.cu_seqlens.data_ptr(), step.seq_slots.data_ptr(), step.kv_lens.data_ptr(),
                                          rows.shape[0], step.n_seqs, nq, nkv, dim, vdim, padded, page_size, int(bool(write_kv)),
-                                         dtype_code(q_out.dtype), _stream()), "conv_attention_inputs")
+                                         int(bool(head_norm)), dtype_code(q_out.dtype), _stream()), "conv_attention_inputs")
 
 
 def conv_state_update(state, rows, bias, taps, step, channels):

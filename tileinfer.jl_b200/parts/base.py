@@ -23,6 +23,8 @@ Interfaces (duck-typed; the base classes document them):
   ``forward(x, h, step, cache, next_norm, h_out)``.
 * ``TokenInput(spec, tensors, rt)`` (``parts/token_input.py``): ``forward(h, step) -> y`` and a ``norm`` through which a
   block that knows of it adds y to the stream at the end of the layer.
+* ``PassInput(spec, tensors, rt)`` (``parts/pass_input.py``): ``begin(x0)`` after the embedding and ``forward(x)`` before each
+  pass over a stretch of layers that runs several times, rewriting the stream from itself and the embedding's output.
 * ``Embedding(model_spec, tensors, rt)`` and ``Head(model_spec, tensors, rt, embedding)``: the two ends of the
   model (``ModelSpec.embedding_kind`` / ``head_kind``), so that an embedding multiplier or a scaled or capped
   logit is a registered part, not an edit of the decoder.
@@ -141,7 +143,7 @@ class Head(Part):
 
 
 _REGISTRIES: Dict[str, Dict[str, Any]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
-                                          "embedding": {}, "head": {}, "token_input": {}}
+                                          "embedding": {}, "head": {}, "token_input": {}, "pass_input": {}}
 
 
 def _register(family: str, kind: str, cls):

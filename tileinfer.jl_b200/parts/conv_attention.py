@@ -6,9 +6,13 @@ Per token, from the mixer's input h (every step optional, by the record):
     u = W h + b                      for q [heads, dim], k [kv_heads, dim], v [kv_heads, value_dim]          (``bias``)
     y_t = sum_j c[:, j] * u_(t - taps + 1 + j)       per channel, zeros before the sequence's start             (``conv_taps``)
     q, k <- y / rms(y) * w           over the WHOLE row of q, and of k, before the heads are split              (``row_norm``)
+                                     or, with ``head_norm`` too, every head by itself with one weight [dim] per projection
     q, k <- rotation of the first rotary_dim elements of every head (the position encoding's)
     p_ij = exp(scale * q_i . k_j) / (sum_(j' <= i) exp(scale * q_i . k_j') + exp(sink_head))                    (``sink``)
-    out = Wo ( concat_heads(sum_j p_ij v_j) * sigmoid(Wg h) )                                                   (``gate``)
+    out = Wo ( concat_heads(sum_j p_ij v_j) * sigmoid(Wg h) ) + bo                                  (``gate``, ``out_bias``)
+
+The output's bias is not added here: the mixer offers it as ``out_bias`` to the block, whose kernel adds it where it reads the
+product (a block that does not know of it refuses the mixer).
 
 A sequence keeps its keys (after convolution, norm and rotation) and values (after convolution) in pages, and the last
 taps - 1 rows u as a small fixed-size state: the mixer asks the cache for both. With ``kv_source`` the layer has no key and value
@@ -18,7 +22,7 @@ Keys and values of different sizes share the paged attention kernels by filling 
 (a zero adds nothing to a score, and the outputs beyond value_dim are dropped by the gate's kernel).
 
 Record: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``, ``window``, ``kv_source``, ``qk_norm_eps`` and the options
-``value_dim``, ``conv_taps`` (0: none), ``bias``, ``row_norm``, ``sink``, ``gate``.
+``value_dim``, ``conv_taps`` (0: none), ``bias``, ``out_bias``, ``row_norm``, ``head_norm``, ``sink``, ``gate``.
 """
 from __future__ import annotations
 
@@ -59,6 +63,8 @@ class ConvAttention(Mixer):
         self.channels = self.nq * self.dim + (self.nkv * (self.dim + self.vdim) if self.own_kv else 0)
         self.bias = torch.cat([get(n[k] + n["bias_suffix"]) for k in kinds]).contiguous() if self.bias_on else None
         self.conv = torch.cat([get(n[k] + n["conv_suffix"]) for k in kinds], 0).contiguous() if self.taps else None
+        self.head_norm = bool(o.get("head_norm", False))
+        self.out_bias = get(n["o"] + n["bias_suffix"]) if o.get("out_bias", False) else None
         self.q_norm = get(n["q"] + n["norm_suffix"]) if self.row_norm else None
         self.k_norm = get(n["k"] + n["norm_suffix"]) if self.row_norm and self.own_kv else None
         self.sink = rt.param(tensors[p + n["sink"]], keep_dtype=True).float().contiguous() if self.sink_on else None
@@ -79,6 +85,8 @@ class ConvAttention(Mixer):
         if spec.kv_source is None:
             rows.update({"k": G * D, "v": G * V})
         out = [TensorDecl(p + n["o"], (W, H * V), std(H * V))]
+        if o.get("out_bias", False):
+            out.append(TensorDecl(p + n["o"] + n["bias_suffix"], (W,), ("normal", 0.1)))
         for k, r in rows.items():
             out.append(TensorDecl(p + n[k], (r, W), std(W)))
             if bias:
@@ -86,7 +94,7 @@ class ConvAttention(Mixer):
             if taps:
                 out.append(TensorDecl(p + n[k] + n["conv_suffix"], (r, taps), ("const_plus_normal", 1.0 / taps, 0.3)))
             if row_norm and k != "v":
-                out.append(TensorDecl(p + n[k] + n["norm_suffix"], (r,), ("one_plus_normal", 0.1)))
+                out.append(TensorDecl(p + n[k] + n["norm_suffix"], (D if o.get("head_norm", False) else r,), ("one_plus_normal", 0.1)))
         if sink:
             out.append(TensorDecl(p + n["sink"], (H,), ("normal", 1.0), keep_dtype=True))
         if gate:
@@ -116,7 +124,8 @@ class ConvAttention(Mixer):
         q = rt.buffer("attention.q", (n, nq, Dp))
         meta = step.group(cache.group_index)
         ops.conv_attention_inputs(rows, self.bias, self.conv, self.taps, cache.state, self.q_norm, self.k_norm, s.qk_norm_eps, self.rotation,
-                                  q, cache.k, cache.v, step, meta.slot_mapping, nq, nkv, D, V, Dp, cache.page_size, write_kv=self.own_kv)
+                                  q, cache.k, cache.v, step, meta.slot_mapping, nq, nkv, D, V, Dp, cache.page_size, write_kv=self.own_kv,
+                                  head_norm=self.head_norm)
         if self.taps > 1:
             ops.conv_state_update(cache.state, rows, self.bias, self.taps, step, C)
         attn = rt.buffer("attention.out", (n, nq * Dp))

@@ -7,9 +7,11 @@ tied head is the embedding table itself (src/hub/loader.jl:157-163).
 """
 from __future__ import annotations
 
+import torch
+
 from ..config.spec import ModelSpec, TensorDecl
 from ..kernels import ops
-from .base import Embedding, Head, register_embedding, register_head
+from .base import CacheRequest, Embedding, Head, register_embedding, register_head
 from .linear import Linear
 
 
@@ -77,4 +79,40 @@ class TokenEmbedding32(Embedding):
 
     def forward_step(self, step, out, status):
         ops.embed_positions32(out, self.table, None, step.token_ids, step.positions, status)
+        return out
+
+
+@register_embedding("scaled_pair32")
+class ScaledPairEmbedding(Embedding):
+    """x = scale * E[token] + G[(previous token * a + token * b) mod buckets], written to a 32-bit stream. G has one more row
+    than ``buckets``, which a sequence's first token takes. The options of the ModelSpec: ``embed_scale``; ``pair_table`` (the
+    name of G; absent: no second table), ``pair_buckets``, ``pair_mul_prev`` (a), ``pair_mul_cur`` (b).
+
+    The previous token of a step's first token is the last token of the step before: the part asks the cache for one 32-bit
+    integer per sequence (``cache_request``), reads it where a sequence continues and rewrites it after every step."""
+
+    def __init__(self, spec: ModelSpec, tensors, rt):
+        o = spec.options
+        self.table = rt.param(tensors[spec.embed_name])
+        self.scale = float(o.get("embed_scale", 1.0))
+        self.pair = rt.param(tensors[o["pair_table"]]) if o.get("pair_table") else None
+        self.buckets, self.mul_prev, self.mul_cur = (int(o.get(k, 0)) for k in ("pair_buckets", "pair_mul_prev", "pair_mul_cur"))
+
+    @classmethod
+    def tensors(cls, spec: ModelSpec):
+        o = spec.options
+        out = [TensorDecl(spec.embed_name, (spec.vocab_size, spec.hidden_size), ("normal", o.get("embed_init_std", spec.init_std)))]
+        if o.get("pair_table"):
+            out.append(TensorDecl(o["pair_table"], (int(o["pair_buckets"]) + 1, spec.hidden_size), ("normal", o.get("pair_init_std", spec.init_std))))
+        return out
+
+    def cache_request(self):
+        return CacheRequest("state", shape=(1,), dtype=torch.int32) if self.pair is not None else None
+
+    def forward_step(self, step, out, status, cache=None):
+        last = cache.state.view(-1) if cache is not None else None
+        ops.embed_bigram32(out, self.table, self.pair, step.token_ids, step.positions, step.tok_slot, last, self.scale, self.buckets,
+                           self.mul_prev, self.mul_cur, status)
+        if last is not None:
+            ops.last_token_update(last, step)
         return out

@@ -61,14 +61,15 @@ class XieluMLP(FeedForward):
 
 @register_feed_forward("gelu_mlp")
 class GeluMLP(FeedForward):
-    """down(act(up h)), no gate and no biases; ``options["activation"]``: "gelu_erf" (the exact form) or "gelu_tanh"."""
+    """down(act(up h)), no gate and no biases; ``options["activation"]``: "gelu_erf" (the exact form), "gelu_tanh" or "relu2"
+    (the squared rectifier max(z, 0)^2)."""
 
     def __init__(self, spec: FeedForwardSpec, tensors, rt):
         self.spec, self.rt = spec, rt
         n, p = spec.tensor_names, spec.prefix
         self.up = Linear(rt.param(tensors[p + n["up"]]), rt, "up")
         self.down = Linear(rt.param(tensors[p + n["down"]]), rt, "down")
-        kinds = {"gelu_erf": ops.EPI_GELU_ERF, "gelu_tanh": ops.EPI_GELU_TANH}
+        kinds = {"gelu_erf": ops.EPI_GELU_ERF, "gelu_tanh": ops.EPI_GELU_TANH, "relu2": ops.EPI_RELU2}
         act = spec.options.get("activation", "gelu_erf")
         if act not in kinds:
             raise ValueError(f"gelu_mlp: activation {act!r} (known: {', '.join(kinds)})")

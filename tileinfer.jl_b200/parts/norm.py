@@ -66,13 +66,28 @@ class RMSNorm32(Norm):
         ops.sum_add_norm32(x, d1, d2, out, self.weight, self.eps, self.offset)
         return out
 
-    def branch_add(self, x, delta, mult, h=None, next_norm=None):
+    def branch_add(self, x, delta, mult, h=None, next_norm=None, bias=None):
+        """``bias`` [size]: a vector added to ``delta`` before its norm (the bias of the product that made ``delta``)."""
         out_norm = next_norm.out_args() if next_norm is not None else None
         if isinstance(delta, GatheredRows):
-            ops.branch_norm_add32(x, delta.rows, self.weight, self.eps, mult, self.offset, h, out_norm, gather=delta.index)
+            ops.branch_norm_add32(x, delta.rows, self.weight, self.eps, mult, self.offset, h, out_norm, gather=delta.index, bias=bias)
         else:
-            ops.branch_norm_add32(x, delta, self.weight, self.eps, mult, self.offset, h, out_norm)
+            ops.branch_norm_add32(x, delta, self.weight, self.eps, mult, self.offset, h, out_norm, bias=bias)
         return h
+
+
+@register_norm("layernorm32")
+class LayerNorm32(RMSNorm32):
+    """Layer norm with a weight and no bias, in 32-bit with one rounding at the end: y = (x - mean(x)) / sqrt(var(x) + eps) * w,
+    var the mean of the squared deviations. The same kernels as :class:`RMSNorm32` with the "centred" flag, so it serves the
+    same blocks (``forward``, ``branch_add``, and as the ``next_norm`` of another norm's ``branch_add``)."""
+
+    def __init__(self, spec: NormSpec, tensors, rt):
+        super().__init__(spec, tensors, rt)
+        self.offset = ops.NORM_CENTRED | (ops.NORM_OFFSET if spec.options.get("offset", False) else 0)
+
+    def sum_add(self, x, d1, d2, out):
+        raise NotImplementedError("layernorm32 does not serve blocks that add two sublayers' outputs at once")
 
 
 class GatheredRows:
