@@ -6,6 +6,7 @@ model with random weights (bfloat16), plus prefill throughput and roofline fract
     python bench.py --preset 8b-long | 70b        (the other two sizes the reference names; a line each)
     python bench.py --preset vogilix [--timeline]  (the Vogilix design at two sizes beside Apertus layers of equal size)
     python bench.py --preset zudepel [--timeline]  (the Zudepel design at two sizes beside Vogilix layers of equal size)
+    python bench.py --preset sozanex [--timeline]  (the Sozanex design at two sizes beside Vogilix layers of equal size)
 
 Prints one JSON line. A "step" is one decode step of the whole batch (default batch 8, every
 sequence after 1,023 cached positions, context 4,096). ``value`` is decoded tokens per second
@@ -526,6 +527,89 @@ def run_zudepel(args, pk, pk_source):
     return 0
 
 
+def sozanex_config(size: str, runs: int):
+    """Layers of a real model's sizes: latent-attention and windowed grouped-query attention layers in turn, every one with a dense
+    squared-rectifier feed-forward; layers 1 and 2 run twice (the loop), so ``runs`` layer runs come from ``runs - 2`` layers."""
+    w, heads, dim, q_rank, kv_rank, window, ff, vocab, buckets = {
+        "mid": (2048, 16, 64, 768, 96, 1024, 8192, 32768, 32749),
+        "wide": (4096, 32, 128, 1536, 192, 2048, 12288, 65536, 65521)}[size]
+    rot = dim // 2
+    latent = {"dim": dim, "heads": heads, "kv_rank": kv_rank, "q_rank": q_rank, "rot_dim": rot, "scale": (dim + rot) ** -0.5, "vdim": dim,
+              "rot": {"base": 10000.0, "dims": rot, "scaling": {"factor": 16.0, "fast": 32.0, "original": 4096, "slow": 1.0}}}
+    attn = {"dim": dim, "heads": heads, "kv_heads": heads // 4, "mask": {"size": window}, "scale": dim ** -0.5, "vdim": dim,
+            "rot": {"base": 500000.0, "dims": rot, "scaling": {"factor": 8.0, "high": 4.0, "low": 1.0, "original": 8192}}}
+    n = max(runs - 2, 3)
+    layers = [{"mixer": latent if i % 2 == 0 else attn, "mlp": {"ff": ff, "kind": "dense"}, "type": "latent_attention" if i % 2 == 0 else "attention"}
+              for i in range(n)]
+    return {"architecture": "Sozanex", "vocab": vocab, "width": w, "norm": {"eps": 1e-5}, "layers": layers,
+            "embedding": {"scale": float(w) ** 0.5, "bigram": {"buckets": buckets, "mul_prev": 8191, "mul_cur": 31}},
+            "loop": {"start": 1, "stop": 3, "times": 2}}
+
+
+def vogilix_dense_twin(size: str, layers: int):
+    """Vogilix layers beside a Sozanex configuration: the same width, depth (layer runs), heads, head size, query rank, cached row
+    per position (latent + rotated part against latent), window and vocabulary, with the dense feed-forward of the same size in
+    every layer (two matrices, as there)."""
+    v = vogilix_config(size, layers)
+    dense = v["layers"][0]["mlp"]
+    for l in v["layers"]:
+        l["mlp"] = dict(dense)
+    return v
+
+
+def run_sozanex(args, pk, pk_source):
+    """Prefill and decode throughput of the Sozanex design at two sizes, each beside Vogilix layers of the same width, depth, heads
+    and feed-forward size (the library's closest model: latent attention and sublayer-output norms on a 32-bit stream); with
+    --timeline also the per-kernel device times of one prompt step and one decode step of the Sozanex model (stderr)."""
+    import torch
+    from tileinfer_b200.config import config_from_dict
+    from tileinfer_b200.engine import Engine
+    runs = args.layers or 8
+    steps, warmup = max(8, min(args.steps, 32)), max(args.warmup, 3)
+    clocks = ClockSampler()
+    clocks.start()
+    out = []
+    for size in ("mid", "wide"):
+        for name, raw in (("sozanex", sozanex_config(size, runs)), ("vogilix", vogilix_dense_twin(size, runs))):
+            cfg = config_from_dict(raw)
+            engine = Engine.random(cfg, seed=0, dtype=args.dtype, max_context=4096, max_seqs=64, max_tokens=64 * 1280,
+                                   max_step_tokens=8192)
+            row = {"size": size, "model": name, "layer_runs": len(cfg.model_spec().order), "weights_gb": round(engine.weight_bytes() / 1e9, 3),
+                   "cache_bytes_per_position": engine.kv_bytes_per_position()}
+            for tokens in (512, 2048):
+                ms = time_prefill(engine, tokens, cfg.vocab_size, reps=3)
+                row[f"prefill_{tokens}_ms"] = round(ms, 3)
+                row[f"prefill_{tokens}_tok_s"] = round(tokens * 1000.0 / ms, 1)
+            for b in (1, 8, 64):
+                ms, _, launches = time_decode(engine, b, steps, warmup, cfg.vocab_size, count_launches=True)
+                row[f"decode_b{b}_ms"] = round(ms, 4)
+                row[f"decode_b{b}_tok_s"] = round(b * 1000.0 / ms, 1)
+                row[f"decode_b{b}_launches"] = launches
+            engine.check_health()
+            out.append(row)
+            del engine
+            torch.cuda.empty_cache()
+    clock_info = clocks.stop()
+    if args.timeline:
+        from tileinfer_b200.kernels import microbench
+        import contextlib
+        with contextlib.redirect_stdout(sys.stderr):
+            for size in ("mid", "wide"):
+                for name, raw in (("sozanex", sozanex_config(size, 5)), ("vogilix", vogilix_dense_twin(size, 5))):
+                    cfg = config_from_dict(raw)
+                    print(f"--- {size} {name}: prompt of 2,048 tokens")
+                    microbench.timeline(1, 0, prefill_tokens=2048, config=cfg, first=70 if name == "sozanex" else 1)
+                    for b in (8, 64):
+                        print(f"--- {size} {name}: decode step of batch {b}")
+                        microbench.timeline(b, 0, config=cfg, first=70 if (b == 8 and name == "sozanex") else 1)
+    print(json.dumps({"metric": "prefill and decode of the Sozanex design beside Vogilix layers of equal size", "n_gpus": 1,
+                      "steps": steps, "warmup": warmup, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+                      "data": "synthetic: random weights, uniform random token ids",
+                      "config": {"cached_positions": CACHED, "peaks": pk_source, "l2": "every step reads more weights than L2 holds"},
+                      "clocks": clock_info, "rows": out}))
+    return 0
+
+
 def flops_prefill(cfg, n_layers, tokens):
     H, I, D = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
@@ -554,7 +638,7 @@ def main(argv=None) -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick checks)")
     ap.add_argument("--timeline", action="store_true", help="--preset vogilix: per-kernel device times of its steps, on stderr")
-    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b", "sweep", "vogilix", "zudepel"],
+    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b", "sweep", "vogilix", "zudepel", "sozanex"],
                     help="8b: the headline line (default); 8b-long: 8 unequal sequences of up to 32,768 positions; "
                          "70b: Apertus-70B sizes, 141 GB of weights")
     args = ap.parse_args(argv)
@@ -580,6 +664,8 @@ def main(argv=None) -> int:
         return run_sweep(args, *peaks())
     if args.preset == "vogilix":
         return run_vogilix(args, *peaks())
+    if args.preset == "sozanex":
+        return run_sozanex(args, pk, pk_source)
     if args.preset == "zudepel":
         return run_zudepel(args, *peaks())
     cfg_dict = dict(APERTUS_8B)
