@@ -665,7 +665,7 @@ def main(argv=None) -> int:
     if args.preset == "vogilix":
         return run_vogilix(args, *peaks())
     if args.preset == "sozanex":
-        return run_sozanex(args, pk, pk_source)
+        return run_sozanex(args, *peaks())
     if args.preset == "zudepel":
         return run_zudepel(args, *peaks())
     cfg_dict = dict(APERTUS_8B)

@@ -26,13 +26,11 @@ def attention(heads, kv_heads, dim, vdim, scale, mlp, window=None, rot=None, sca
     return {"mixer": m, "mlp": mlp, "type": "attention"}
 
 
-def latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, mlp, base=10000.0, scaling=None, window=None):
+def latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, mlp, base=10000.0, scaling=None):
     m = {"dim": dim, "heads": heads, "kv_rank": kv_rank, "q_rank": q_rank, "scale": scale, "vdim": vdim, "rot_dim": rot_dim,
          "rot": {"base": base, "dims": rot_dim}}
     if scaling:
         m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
-    if window:
-        m["mask"] = {"size": window}
     return {"mixer": m, "mlp": mlp, "type": "latent_attention"}
 
 

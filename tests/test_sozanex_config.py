@@ -80,6 +80,7 @@ def test_what_is_refused():
     broken(lambda c: c["layers"][1]["mixer"]["rot"].update(dims=7))
     broken(lambda c: c["layers"][0]["mixer"]["rot"].update(dims=8))          # the rotated part and its rotation differ
     broken(lambda c: c["layers"][0]["mixer"].pop("q_rank"))
+    broken(lambda c: c["layers"][0]["mixer"].update(mask={"size": 8}))       # only the attention mixer has a window
     broken(lambda c: c["layers"][2]["mlp"].update(kind="moe"))
     broken(lambda c: c["loop"].update(stop=5))
     broken(lambda c: c["loop"].update(start=3))

@@ -119,22 +119,20 @@ class LatentAttentionConfig:
     q_rank: int
     kv_rank: int
     scale: float
-    window: Optional[int]
     rot: Optional[RotationConfig]
 
     @classmethod
     def from_dict(cls, m, where):
-        rot, mask = m.get("rot"), m.get("mask")
+        rot = m.get("rot")
         out = cls(int(_need(m, "heads", where)), int(_need(m, "dim", where)), int(m.get("rot_dim") or 0), int(_need(m, "vdim", where)),
                   int(_need(m, "q_rank", where)), int(_need(m, "kv_rank", where)), float(_need(m, "scale", where)),
-                  None if not mask else int(_need(mask, "size", where + ".mask")),
                   None if not rot else RotationConfig.from_dict(rot, where + ".rot", yarn=True))
         if min(out.heads, out.dim, out.vdim, out.q_rank, out.kv_rank) < 1 or out.rot_dim < 0:
             raise ConfigError(f"{where}: heads, dim, vdim, q_rank and kv_rank must be positive")
         if (out.rot_dim > 0) != (out.rot is not None) or (out.rot is not None and out.rot.dims != out.rot_dim):
             raise ConfigError(f"{where}: the rotated part of {out.rot_dim} elements needs a rotation of as many (rot.dims)")
-        if out.window is not None and out.window < 1:
-            raise ConfigError(f"{where}.mask.size must be positive")
+        if m.get("mask"):
+            raise ConfigError(f"{where}.mask: this mixer sees every earlier position; only the attention mixer has a window")
         return out
 
     def to_dict(self):
@@ -142,8 +140,6 @@ class LatentAttentionConfig:
         if self.rot_dim:
             d["rot_dim"] = self.rot_dim
             d["rot"] = self.rot.to_dict()
-        if self.window is not None:
-            d["mask"] = {"size": self.window}
         return d
 
 
@@ -290,7 +286,7 @@ class SozanexConfig:
                     position = PositionSpec(kind="rope", head_dim=m.rot_dim, theta=m.rot.base, scaling=m.rot.scaling,
                                             max_positions=self.max_positions, options=rope_options(m.rot.dims, "interleaved"))
                 mixer = MixerSpec(kind="latent_attention", prefix=p + "mix.", hidden_size=W, num_heads=m.heads, num_kv_heads=1,
-                                  head_dim=m.dim, scale=m.scale, window=m.window, position=position,
+                                  head_dim=m.dim, scale=m.scale, window=None, position=position,
                                   tensor_names={"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm",
                                                 "uk": "uk", "uv": "uv", "o": "o", "sink": "sink", "g": "g"},
                                   options={"value_dim": m.vdim, "q_rank": m.q_rank, "kv_rank": m.kv_rank, "latent_norm_eps": eps,

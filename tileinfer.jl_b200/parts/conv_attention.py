@@ -136,7 +136,10 @@ class ConvAttention(Mixer):
         if not done:
             ops.attention_plain(attn, q, cache.k, cache.v, meta.block_table, step.tok_slot, step.positions, s.scale, nq, nkv, Dp,
                                 cache.page_size, window=s.window or 0, sink=self.sink)
-        y = rt.buffer("conv_attention.gated", (n, nq * V))
-        ops.sigmoid_gate(y, attn, rows[:, C:] if self.gated else None, nq, V, Dp)
+        if self.gated or Dp != V:
+            y = rt.buffer("conv_attention.gated", (n, nq * V))
+            ops.sigmoid_gate(y, attn, rows[:, C:] if self.gated else None, nq, V, Dp)
+        else:
+            y = attn                                # no gate and no filling to drop: the heads' outputs as they are
         out = rt.buffer("mixer.delta", (n, s.hidden_size))
         return self.o.forward(y, out, allow_partials=True)
