@@ -449,8 +449,8 @@ def test_small_kernels_alone(dtype):
 
 
 def test_the_pass_input_reads_the_stream_and_the_embedding():
-    """x <- W [x; x0]: with W = [2 I, 3 I] the stream after the pass input of a model without layers' contributions would be
-    2 x + 3 x0; checked on the part alone, for rows that differ in x and x0."""
+    """s' = P concat(s, e): with P = [2 I, 3 I] the stream after the pass input of a model without layers' contributions would be
+    2 s + 3 e; checked on the part alone, for rows that differ in x and x0."""
     from tileinfer_b200.config.spec import PassInputSpec
     from tileinfer_b200.parts import Runtime, lookup
     for T in (torch.float32, torch.bfloat16):

@@ -7,7 +7,7 @@ nowhere else:
 * the stream starts as ``embedding.scale`` times the token's embedding row plus, with ``embedding.bigram``, a row of a second
   table chosen by a hash of the token and the one before it (an extra last row for a sequence's first token); it is kept in 32-bit;
 * ``loop``: the layers ``start .. stop - 1`` run ``times`` times in a row with the same weights (every run with a cache of its
-  own), and before the first layer of every such pass the stream x becomes W [x; x0], x0 being the embedding's output;
+  own), and before the first layer of every such pass the stream s becomes P concat(s, e), e being the embedding's output;
 * a layer has a layer norm (a weight, no bias) before AND after each sublayer: x += n1b(mixer(n1(x))); x += n2b(ff(n2(x)));
   the model ends with such a norm and the head;
 * mixer ``attention``: grouped-query attention (``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``) with biases on q, k, v and

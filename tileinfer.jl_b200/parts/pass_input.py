@@ -1,6 +1,6 @@
 """What rewrites the residual stream before a pass over a stretch of layers that runs several times with the same weights.
 
-``concat_linear``: x <- W [x; x0] for W [hidden, 2 hidden] (x's columns first), x0 being the embedding's output of the same
+``concat_linear``: s' = P concat(s, e) for P [hidden, 2 hidden] (the stream's columns first), e being the embedding's output of the same
 token. The stream is 32-bit; the product's operands are the two rows rounded to the products' element type, side by side in one
 buffer, and its sums go back to the stream in 32-bit.
 
