@@ -2,6 +2,7 @@
 model declares, the order of the layer runs, the rotation tables, the round trip through a model folder, what the cache is
 asked for, and the plain implementation's own pieces."""
 import copy
+import json
 import math
 
 import pytest
@@ -138,3 +139,18 @@ def test_plain_pieces():
     r = plain.rotate(torch.tensor([[[1.0, 0.0, 0.0, 1.0]], [[1.0, 0.0, 0.0, 1.0]]], dtype=torch.float64), [math.pi / 2, math.pi], True)
     assert torch.allclose(r[1, 0], torch.tensor([0.0, 1.0, -0.0, -1.0], dtype=torch.float64), atol=1e-12)
     assert [i for i, _ in plain.layer_runs(sc.CASE_A)] == [0, 1, 0, 1, 0, 1, 2]
+
+
+def test_the_command_line_writes_a_model_folder_of_this_design(tmp_path, capsys):
+    """``tileinfer random config.json out`` goes through the registry: a Sozanex config.json gives a folder that loads back, with
+    the loop's input projection, the second table's extra row and the latent layer's tensors in it."""
+    from tileinfer_b200.cli import cli
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(sc.CASE_A))
+    out = tmp_path / "model"
+    assert cli(["random", str(cfg_path), str(out), "--seed", "3"]) == 0
+    cfg, W = sc.load_folder(str(out))
+    assert cfg["architecture"] == "Sozanex" and cfg["loop"] == {"start": 0, "stop": 2, "times": 3}
+    assert W["loop.in"].shape == (52, 104) and W["bigram"].shape == (98, 52)
+    assert W["l1.mix.dkv"].shape == (26 + 6, 52) and W["l1.mix.sink"].shape == (3,) and W["l0.mix.q.norm"].shape == (10,)
+    assert W["l0.mix.o.b"].shape == (52,) and "l1.mlp.up" not in W
