@@ -1,6 +1,7 @@
 from .apertus import ApertusConfig, ConfigError, parse_rope_scaling
 from .registry import (Architecture, config_from_dict, load_config, register_architecture,
                        registered_architectures, resolve_architecture)
+from .fasodra import FasodraConfig
 from .sozanex import SozanexConfig
 from .spec import (FeedForwardSpec, LayerSpec, Llama3RopeScaling, MixerSpec, ModelSpec, NormSpec, PassInputSpec, PositionSpec,
                    TensorDecl, TokenInputSpec, YarnRopeScaling)

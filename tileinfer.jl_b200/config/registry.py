@@ -13,6 +13,7 @@ from dataclasses import dataclass
 from typing import Any, Callable, Dict, Mapping, Optional
 
 from .apertus import ApertusConfig, ConfigError
+from .fasodra import FasodraConfig
 from .vogilix import VogilixConfig
 from .sozanex import SozanexConfig
 from .zudepel import ZudepelConfig
@@ -75,3 +76,4 @@ register_architecture(ApertusConfig.architecture, ApertusConfig, model_type=Aper
 register_architecture(VogilixConfig.architecture, VogilixConfig, model_type=VogilixConfig.model_type)
 register_architecture(ZudepelConfig.architecture, ZudepelConfig, model_type=ZudepelConfig.model_type)
 register_architecture(SozanexConfig.architecture, SozanexConfig, model_type=SozanexConfig.model_type)
+register_architecture(FasodraConfig.architecture, FasodraConfig, model_type=FasodraConfig.model_type)

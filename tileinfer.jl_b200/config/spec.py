@@ -32,6 +32,9 @@ class TensorDecl:
     # When True the checkpoint may hold more leading rows than ``shape[0]``; the first
     # ``shape[0]`` are used (an embedding table padded beyond the vocabulary).
     allow_extra_rows: bool = False
+    # Dimensions whose extent the checkpoint decides (a table's number of rows, a low rank that no configuration key gives):
+    # the loader accepts any extent there and the part reads it from the tensor; ``shape`` holds what the random-weights mode makes.
+    free_dims: Tuple[int, ...] = ()
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,8 @@
 // Element-wise activations that are not a product's epilogue.
 //
 //   gelu                    y = T(gelu(x)), the exact form 0.5 x (1 + erf(x / sqrt 2)) or the tanh form
-//                           0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3)))
+//                           0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))); the same kernel applies the squared rectifier
+//                           max(x, 0)^2 (form 2) and tanh (form 3)
 //   gated_token_embedding   g[t, j] = T(gelu_tanh(g[t, j]) * table[id[t], first + j]): a gate computed from the stream
 //                           times the token's own vector, one slice of a table with a row per token id
 //   gated_unit_limit        y[t, j] = T(a * sigmoid(slope * a) * (b + shift)), a = min(gu[t, j], limit),
@@ -10,7 +11,17 @@
 
 #define ACT_GELU_ERF 0
 #define ACT_GELU_TANH 1
+#define ACT_RELU2 2
+#define ACT_TANH 3
 
+__device__ __forceinline__ float act_value(float z, int kind) {
+    if (kind == ACT_RELU2) {
+        const float r = fmaxf(z, 0.f);
+        return r * r;
+    }
+    if (kind == ACT_TANH) return tanhf(z);
+    return kind == ACT_GELU_TANH ? gelu_tanh_value(z) : gelu_erf_value(z);
+}
 
 template <typename T>
 __global__ void gelu_kernel(T* out, const T* in, size_t count, int kind) {
@@ -19,7 +30,7 @@ __global__ void gelu_kernel(T* out, const T* in, size_t count, int kind) {
     pdl_enter();
     for (; i < count; i += stride) {
         const float z = to_f32(__ldcg(in + i));
-        out[i] = from_f32<T>(kind == ACT_GELU_TANH ? gelu_tanh_value(z) : gelu_erf_value(z));
+        out[i] = from_f32<T>(act_value(z, kind));
     }
 }
 
@@ -33,14 +44,14 @@ __global__ void gelu_vec_kernel(T* out, const T* in, size_t vecs, int kind) {
         Vec16<T> v;
         v.load_cg(in + i * N);
 #pragma unroll
-        for (int e = 0; e < N; ++e) v.v[e] = kind == ACT_GELU_TANH ? gelu_tanh_value(v.v[e]) : gelu_erf_value(v.v[e]);
+        for (int e = 0; e < N; ++e) v.v[e] = act_value(v.v[e], kind);
         v.store(out + i * N);
     }
 }
 
 extern "C" int ti_gelu(void* out, const void* in, long long count, int kind, int dtype, cudaStream_t stream) {
     if (count == 0) return 0;
-    TI_REQUIRE(kind == ACT_GELU_ERF || kind == ACT_GELU_TANH, "gelu: unknown form %d", kind);
+    TI_REQUIRE(kind >= ACT_GELU_ERF && kind <= ACT_TANH, "gelu: unknown form %d", kind);
     TI_DISPATCH_DTYPE(dtype, {
         constexpr int N = Vec16<T>::N;
         const bool vec = count % N == 0 && aligned16(out) && aligned16(in);

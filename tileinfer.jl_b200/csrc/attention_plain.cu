@@ -28,7 +28,8 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
                                        const T* v_cache, const int* block_table,
                                        int table_stride, const int* tok_slot,
                                        const int* positions, float scale, int nq, int nkv, int D,
-                                       int page_size, int window, const float* __restrict__ sink) {
+                                       int page_size, int window, const float* __restrict__ sink, int chunk,
+                                       const float* __restrict__ dist_bias, int bias_len) {
     extern __shared__ float smem[];
     float* qs = smem;                          // [AP_HEADS][D]
     float* sc = smem + AP_HEADS * D;           // [AP_HEADS][AP_CHUNK]
@@ -54,7 +55,9 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
 #pragma unroll
         for (int i = 0; i < ACC; ++i) acc[h][i] = 0.f;
     }
-    const int first = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
+    int first = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
+    // Chunked visibility: only the keys of the query's own chunk of `chunk` positions, counted from the sequence's start.
+    if (chunk > 0) first = max(first, (p / chunk) * chunk);
     const bool wide = D % Vec16<T>::N == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0;
     // Chunk borders are multiples of AP_CHUNK in absolute positions.
     for (int c0 = (first / AP_CHUNK) * AP_CHUNK; c0 <= p; c0 += AP_CHUNK) {
@@ -92,6 +95,8 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
             for (int h = 0; h < AP_HEADS; ++h)
                 if (h < heads) {
                     s[h] *= scale;
+                    // A learned bias per (head, distance), added after the scale; distances beyond the table take its last entry.
+                    if (dist_bias != nullptr) s[h] += dist_bias[(size_t)(h0 + h) * bias_len + min(p - j, bias_len - 1)];
                     sc[h * AP_CHUNK + j - c0] = s[h];
                     cmax[h] = fmaxf(cmax[h], s[h]);
                 }
@@ -147,11 +152,14 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
     }
 }
 
-extern "C" int ti_attention_plain(void* out, const void* q, const void* k_cache, const void* v_cache,
-                                  const int* block_table, int table_stride, const int* tok_slot, const int* positions,
-                                  float scale, int n_tokens, int nq, int nkv, int D, int page_size, int window,
-                                  const float* sink, int dtype, cudaStream_t stream) {
+// `chunk` > 0: a key is visible only inside the query's chunk of so many positions; `dist_bias` [nq][bias_len] float: added to
+// the scaled score by the distance between query and key (null: none).
+extern "C" int ti_attention_plain_biased(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                         const int* block_table, int table_stride, const int* tok_slot, const int* positions,
+                                         float scale, int n_tokens, int nq, int nkv, int D, int page_size, int window,
+                                         const float* sink, int chunk, const float* dist_bias, int bias_len, int dtype, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
+    TI_REQUIRE(chunk >= 0 && (dist_bias == nullptr || bias_len > 0), "attention: chunk %d, bias table of %d", chunk, bias_len);
     TI_REQUIRE(D > 0 && D <= AP_MAX_D, "attention: head_dim %d exceeds %d", D, AP_MAX_D);
     TI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads do not divide into %d KV heads", nq, nkv);
     const int sets = (nq / nkv + AP_HEADS - 1) / AP_HEADS;
@@ -160,6 +168,14 @@ extern "C" int ti_attention_plain(void* out, const void* q, const void* k_cache,
     const size_t smem = (size_t)AP_HEADS * (D + AP_CHUNK) * sizeof(float);
     TI_DISPATCH_DTYPE(dtype, (ti_launch(attention_plain_kernel<T>, dim3(grid), dim3(AP_THREADS), smem, stream, 
                                  (T*)out, (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, table_stride,
-                                 tok_slot, positions, scale, nq, nkv, D, page_size, window, sink)));
+                                 tok_slot, positions, scale, nq, nkv, D, page_size, window, sink, chunk, dist_bias, bias_len)));
     return ti_check_launch("attention_plain");
+}
+
+extern "C" int ti_attention_plain(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                  const int* block_table, int table_stride, const int* tok_slot, const int* positions,
+                                  float scale, int n_tokens, int nq, int nkv, int D, int page_size, int window,
+                                  const float* sink, int dtype, cudaStream_t stream) {
+    return ti_attention_plain_biased(out, q, k_cache, v_cache, block_table, table_stride, tok_slot, positions, scale, n_tokens, nq, nkv, D,
+                                     page_size, window, sink, 0, nullptr, 0, dtype, stream);
 }

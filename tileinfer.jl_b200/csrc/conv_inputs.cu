@@ -209,20 +209,22 @@ extern "C" int ti_conv_state_update(float* state, const void* proj, long long ld
 
 // y [n, heads * V] = T(attn[n, heads, :V of Dp] * sigmoid(g [n, ldg])): the output gate, which also drops the rows' filling.
 template <typename T>
-__global__ void sigmoid_gate_kernel(T* __restrict__ y, const T* attn, const T* g, long long ldg, int heads, int V, int Dp, size_t count) {
+__global__ void sigmoid_gate_kernel(T* __restrict__ y, const T* attn, const T* g, long long ldg, int heads, int V, int Dp, size_t count,
+                                    int per_head) {
     pdl_enter();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / ((size_t)heads * V);
         const int c = (int)(i % ((size_t)heads * V)), head = c / V, d = c % V;
         float v = to_f32(__ldcg(attn + (t * heads + head) * Dp + d));
-        if (g != nullptr) v = v / (1.0f + expf(-to_f32(__ldcg(g + t * ldg + c))));
+        if (g != nullptr) v = v / (1.0f + expf(-to_f32(__ldcg(g + t * ldg + (per_head ? head : c)))));
         y[i] = from_f32<T>(v);
     }
 }
 
 // The same with 16 bytes of outputs per thread.
 template <typename T>
-__global__ void sigmoid_gate_vec_kernel(T* __restrict__ y, const T* attn, const T* g, long long ldg, int heads, int V, int Dp, size_t vecs) {
+__global__ void sigmoid_gate_vec_kernel(T* __restrict__ y, const T* attn, const T* g, long long ldg, int heads, int V, int Dp, size_t vecs,
+                                        int head_gate) {
     constexpr int N = Vec16<T>::N;
     const int per_head = V / N, per_row = heads * per_head;
     pdl_enter();
@@ -231,7 +233,11 @@ __global__ void sigmoid_gate_vec_kernel(T* __restrict__ y, const T* attn, const 
         const int r = (int)(i % per_row), head = r / per_head, d = (r % per_head) * N;
         Vec16<T> a;
         a.load_cg(attn + (t * heads + head) * Dp + d);
-        if (g != nullptr) {
+        if (g != nullptr && head_gate) {         // one gate for the whole head: g [n, heads]
+            const float s = 1.0f / (1.0f + expf(-to_f32(__ldcg(g + t * ldg + head))));
+#pragma unroll
+            for (int e = 0; e < N; ++e) a.v[e] *= s;
+        } else if (g != nullptr) {
             Vec16<T> gate;
             gate.load_cg(g + t * ldg + head * V + d);
 #pragma unroll
@@ -241,17 +247,18 @@ __global__ void sigmoid_gate_vec_kernel(T* __restrict__ y, const T* attn, const 
     }
 }
 
-extern "C" int ti_sigmoid_gate(void* y, const void* attn, const void* g, long long ldg, int n, int heads, int V, int Dp, int dtype,
+// per_head: g is [n, heads] (rows ldg apart), one gate per head, instead of one per output element.
+extern "C" int ti_sigmoid_gate(void* y, const void* attn, const void* g, long long ldg, int n, int heads, int V, int Dp, int per_head, int dtype,
                                cudaStream_t stream) {
     if (n == 0) return 0;
     TI_DISPATCH_DTYPE(dtype, {
         constexpr int N = Vec16<T>::N;
-        const bool vec = V % N == 0 && Dp % N == 0 && ldg % N == 0 && aligned16(y) && aligned16(attn) && aligned16(g);
+        const bool vec = V % N == 0 && Dp % N == 0 && aligned16(y) && aligned16(attn) && (per_head || (ldg % N == 0 && aligned16(g)));
         const long long count = vec ? (long long)n * heads * (V / N) : (long long)n * heads * V;
         long long blocks = (count + 255) / 256;
         if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
-        if (vec) ti_launch(sigmoid_gate_vec_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)y, (const T*)attn, (const T*)g, ldg, heads, V, Dp, (size_t)count);
-        else ti_launch(sigmoid_gate_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)y, (const T*)attn, (const T*)g, ldg, heads, V, Dp, (size_t)count);
+        if (vec) ti_launch(sigmoid_gate_vec_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)y, (const T*)attn, (const T*)g, ldg, heads, V, Dp, (size_t)count, per_head);
+        else ti_launch(sigmoid_gate_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)y, (const T*)attn, (const T*)g, ldg, heads, V, Dp, (size_t)count, per_head);
     });
     return ti_check_launch("sigmoid_gate");
 }

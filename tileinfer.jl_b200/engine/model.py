@@ -36,6 +36,9 @@ def tensor_declarations(spec: ModelSpec) -> List[TensorDecl]:
             decls += lookup("feed_forward", layer.feed_forward.kind).tensors(layer.feed_forward)
         if layer.token_input is not None:
             decls += lookup("token_input", layer.token_input.kind).tensors(layer.token_input)
+        block_tensors = getattr(lookup("block", layer.block), "tensors", None)
+        if block_tensors is not None:                            # an arrangement with learned tables of its own
+            decls += block_tensors(layer)
     seen, out = set(), []
     for d in decls:
         if d.name not in seen:
@@ -78,7 +81,10 @@ class DecoderModel:
                 extra["mixer_post_norm"] = lookup("norm", layer.mixer_post_norm.kind)(layer.mixer_post_norm, tensors, rt)
             if layer.feed_forward_post_norm is not None:
                 extra["feed_forward_post_norm"] = lookup("norm", layer.feed_forward_post_norm.kind)(layer.feed_forward_post_norm, tensors, rt)
-            self.blocks.append(lookup("block", layer.block)(layer, mixer, ffn, n1, n2, **extra))
+            block_class = lookup("block", layer.block)
+            if getattr(block_class, "tensors", None) is not None:
+                extra.update({"tensors": tensors, "rt": rt})
+            self.blocks.append(block_class(layer, mixer, ffn, n1, n2, **extra))
         self.pass_input = None
         if spec.pass_input is not None:
             self.pass_input = lookup("pass_input", spec.pass_input.kind)(spec.pass_input, tensors, rt)
@@ -90,6 +96,10 @@ class DecoderModel:
         self.status = torch.zeros(1, dtype=torch.int32, device=rt.device)
         # The residual stream has the products' element type unless the architecture keeps it in 32-bit.
         self.stream_dtype = torch.float32 if spec.options.get("residual_dtype") == "float32" else rt.dtype
+        # Copies of the stream that the layers' arrangement keeps side by side (0: one stream); a row of x holds them all.
+        self.streams = int(spec.options.get("streams") or 0)
+        if self.streams and self.stream_dtype != torch.float32:
+            raise ValueError("several copies of the stream are kept in 32-bit")
 
     def _position(self, pspec):
         key = (pspec.kind, pspec.head_dim, pspec.theta, pspec.scaling, pspec.max_positions, tuple(sorted(pspec.options.items())))
@@ -157,7 +167,9 @@ class DecoderModel:
     def _forward(self, step, cache, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         rt, spec = self.rt, self.spec
         n = step.n_tokens
-        x = rt.buffer("model.x", (n, spec.hidden_size), self.stream_dtype)
+        stream = rt.buffer("model.x", (n, max(1, self.streams) * spec.hidden_size), self.stream_dtype)
+        # With copies of the stream the embedding's output is written once and then laid into every copy.
+        x = rt.buffer("model.x0", (n, spec.hidden_size), self.stream_dtype) if self.streams else stream
         h = rt.buffer("model.h", (n, spec.hidden_size))
         embed_step = getattr(self.embedding, "forward_step", None)
         if self._embedding_cache is not None:
@@ -168,6 +180,9 @@ class DecoderModel:
             self.embedding.forward(step.token_ids, x, self.status)
         if self.pass_input is not None:
             self.pass_input.begin(x)
+        if self.streams:
+            ops.streams_begin(stream, x, self.streams)
+            x = stream
         order = spec.order
         self.blocks[order[0]].input_norm.forward(x, h) if order else self.final_norm.forward(x, h)
         for occ, li in enumerate(order):

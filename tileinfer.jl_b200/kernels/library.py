@@ -79,6 +79,7 @@ _SIGNATURES = {
     "ti_add": [_P, _P, _L, _I, _P],
     "ti_attention_inputs": [_P, _L, _P, _I, _L, _P, _P, _P, _P, _P, _F, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_attention_plain": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P, _I, _P],
+    "ti_attention_plain_biased": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P, _I, _P, _I, _I, _P],
     "ti_gemm_plain": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P],
     "ti_argmax": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "ti_sample": [_P, _L, _I, _I, _F, _I, _F, _P, _P, _P, _P, _P],
@@ -189,7 +190,7 @@ _SIGNATURES.update({
     "ti_conv_attention_inputs": [_P, _L, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
                                  _I, _I, _P],
     "ti_conv_state_update": [_P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _P],
-    "ti_sigmoid_gate": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
+    "ti_sigmoid_gate": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     "ti_sum_add_norm32": [_P, _P, _P, _I, _L, _P, _P, _I, _L, _P, _P, _I, _F, _I, _I, _I, _P],
     "ti_router_select": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P],
     "ti_gated_act": [_P, _P, _I, _I, _I, _I, _P],
@@ -202,4 +203,18 @@ _SIGNATURES.update({
     "ti_last_token_update": [_P, _P, _P, _P, _I, _P],
     "ti_cast_rows_ld": [_P, _L, _P, _I, _I, _I, _P],
     "ti_rotate_heads": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+})
+
+# Several copies of the residual stream; recurrences over a matrix state with decays that depend on the token; their inputs and outputs.
+_SIGNATURES.update({
+    "ti_streams_begin": [_P, _P, _I, _I, _I, _P],
+    "ti_streams_read_norm": [_P, _P, _P, _I, _P, _P, _F, _I, _I, _I, _I, _P],
+    "ti_streams_update": [_P, _P, _P, _I, _L, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _P],
+    "ti_decay_scan": [_P, _P, _L, _I, _I, _I, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P],
+    "ti_delta_scan": [_P, _P, _L, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "ti_shift_blend": [_P, _P, _P, _I, _P, _L, _P, _P, _I, _I, _I, _I, _P],
+    "ti_delta_inputs": [_P, _P, _L, _P, _I, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "ti_history_update": [_P, _L, _P, _L, _I, _P, _P, _I, _I, _I, _P],
+    "ti_heads_norm_gate": [_P, _P, _P, _L, _P, _I, _F, _I, _I, _I, _I, _P],
+    "ti_pair_combine": [_P, _P, _P, _I, _L, _P, _P, _I, _L, _P, _P, _I, _F, _F, _F, _I, _I, _I, _P],
 })

@@ -133,10 +133,25 @@ def attention_inputs(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, rota
 
 
 def attention_plain(out, q, k_cache, v_cache, block_table, tok_slot, positions, scale, nq, nkv, head_dim,
-                    page_size, window=0, sink=None):
-    """``sink`` [nq] float32: one more term exp(sink[head]) in every softmax's denominator (no key, no value)."""
+                    page_size, window=0, sink=None, chunk=0, distance_bias=None):
+    """``sink`` [nq] float32: one more term exp(sink[head]) in every softmax's denominator (no key, no value). ``chunk`` > 0: a
+    key is visible only inside the query's chunk of so many positions (counted from the sequence's start). ``distance_bias``
+    [nq, L] float32: entry [head, min(distance, L - 1)] is added to the scaled score."""
     if sink is not None:
         _need(sink, "sink", torch.float32)
+    if chunk or distance_bias is not None:
+        if distance_bias is not None:
+            _need(distance_bias, "distance_bias", torch.float32)
+            if distance_bias.dim() != 2 or distance_bias.shape[0] != nq:
+                raise KernelError(f"attention: bias table {tuple(distance_bias.shape)} for {nq} heads")
+        _need(out, "out"); _need(q, "q", out.dtype); _need(k_cache, "k_cache", out.dtype); _need(v_cache, "v_cache", out.dtype)
+        _need(block_table, "block_table", torch.int32); _need(tok_slot, "tok_slot", torch.int32); _need(positions, "positions", torch.int32)
+        check(lib().ti_attention_plain_biased(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+                                              block_table.stride(0), tok_slot.data_ptr(), positions.data_ptr(), scale, q.shape[0], nq, nkv,
+                                              head_dim, page_size, window or 0, _ptr(sink), int(chunk or 0), _ptr(distance_bias),
+                                              distance_bias.shape[1] if distance_bias is not None else 0, dtype_code(out.dtype), _stream()),
+              "attention_plain")
+        return
     _need(out, "out"); _need(q, "q", out.dtype); _need(k_cache, "k_cache", out.dtype); _need(v_cache, "v_cache", out.dtype)
     _need(block_table, "block_table", torch.int32); _need(tok_slot, "tok_slot", torch.int32)
     _need(positions, "positions", torch.int32)
@@ -524,13 +539,14 @@ def conv_state_update(state, rows, bias, taps, step, channels):
                                      step.seq_slots.data_ptr(), step.n_seqs, channels, dtype_code(rows.dtype), _stream()), "conv_state_update")
 
 
-def sigmoid_gate(y, attn, gate, heads, vdim, padded):
-    """y [n, heads * vdim] = attn [n, heads, padded][..., :vdim] * sigmoid(gate [n, heads * vdim]) (``gate`` None: the copy alone)."""
+def sigmoid_gate(y, attn, gate, heads, vdim, padded, per_head=False):
+    """y [n, heads * vdim] = attn [n, heads, padded][..., :vdim] * sigmoid(gate [n, heads * vdim]) (``gate`` None: the copy alone);
+    ``per_head``: gate is [n, heads], one number for a whole head."""
     _need(y, "y"); _need(attn, "attn", y.dtype)
     if gate is not None:
         _need(gate, "gate", y.dtype, contiguous=False)
     check(lib().ti_sigmoid_gate(y.data_ptr(), attn.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, y.shape[0], heads, vdim,
-                                padded, dtype_code(y.dtype), _stream()), "sigmoid_gate")
+                                padded, int(bool(per_head)), dtype_code(y.dtype), _stream()), "sigmoid_gate")
 
 
 def router_select(h, wr, logits, experts, total, top, ids, scores, pass_weight=None, softmax=True, correction=None, groups=1, keep=1,
@@ -562,3 +578,126 @@ def gated_act(y, gu, kind):
     if tuple(gu.shape) != (n, 2 * ff):
         raise KernelError(f"gated_act: gu {tuple(gu.shape)} for y {tuple(y.shape)}")
     check(lib().ti_gated_act(y.data_ptr(), gu.data_ptr(), n, ff, kind, dtype_code(y.dtype), _stream()), "gated_act")
+
+
+ACT_RELU2, ACT_TANH = 2, 3
+
+
+def tanh(out, x):
+    """out = tanh(x), rounded once."""
+    _need(out, "out"); _need(x, "x", out.dtype)
+    check(lib().ti_gelu(out.data_ptr(), x.data_ptr(), x.numel(), ACT_TANH, dtype_code(out.dtype), _stream()), "tanh")
+
+
+def relu2(out, x):
+    """out = max(x, 0)^2, rounded once."""
+    _need(out, "out"); _need(x, "x", out.dtype)
+    check(lib().ti_gelu(out.data_ptr(), x.data_ptr(), x.numel(), ACT_RELU2, dtype_code(out.dtype), _stream()), "relu2")
+
+
+# ---------------------------------------------------------------- several copies of the residual stream
+def _floats(values):
+    import ctypes
+    values = [float(v) for v in values]
+    return (ctypes.c_float * len(values))(*values)
+
+
+def streams_begin(x, x0, streams):
+    """x [n, streams * size] float32 <- x0 [n, size] in every copy."""
+    _need(x, "x", torch.float32); _need(x0, "x0", torch.float32)
+    n, size = x0.shape
+    check(lib().ti_streams_begin(x.data_ptr(), x0.data_ptr(), n, streams, size, _stream()), "streams_begin")
+
+
+def streams_read_norm(h, x, a, w, b, eps, centred=True):
+    """h = norm(sum_s a[s] x_s) for x [n, S * size] float32, ``a`` [S] float32 on the device; the norm has the weight ``w`` and,
+    if not None, the bias ``b``; ``centred``: a layer norm (mean taken off), else an RMS norm."""
+    _need(h, "h"); _need(x, "x", torch.float32); _need(a, "a", torch.float32); _need(w, "w", h.dtype)
+    n, size = h.shape
+    check(lib().ti_streams_read_norm(h.data_ptr(), x.data_ptr(), a.data_ptr(), a.numel(), w.data_ptr(), _ptr(b), eps, int(bool(centred)), n, size,
+                                     dtype_code(h.dtype), _stream()), "streams_read_norm")
+
+
+def streams_update(x, delta, mix, out, in_next, h, w, b, eps, centred=True):
+    """x_t <- sum_s mix[s][t] x_s + out[t] * delta for the S copies x [n, S * size] float32 (``mix`` [S * S] and ``out`` [S]: host
+    floats, ``out`` already times the branch multiplier); then, with ``h``, h = norm(sum_t in_next[t] x_t) (``in_next`` host floats;
+    the norm as in ``streams_read_norm``). ``delta``: rows [n, size] of h's type, or float32 [s, n, size] that are added up."""
+    _need(x, "x", torch.float32)
+    S = len(out)
+    n = x.shape[0]
+    size = x.shape[1] // S
+    dtype = h.dtype if h is not None else (delta.dtype if delta.dim() == 2 else w.dtype)
+    if h is not None:
+        _need(h, "h"); _need(w, "w", h.dtype)
+    check(lib().ti_streams_update(x.data_ptr(), *_rows_or_partials(delta, dtype, "delta"), _floats(mix), _floats(out),
+                                  _floats(in_next) if in_next is not None else None, S, _ptr(h), _ptr(w), _ptr(b), eps, int(bool(centred)), n, size,
+                                  dtype_code(dtype), _stream()), "streams_update")
+
+
+# ---------------------------------------------------------------- recurrences with decays that depend on the token
+def shift_blend(out, h, mu, prev, step):
+    """out [K, n, W] = h + (row before - h) * mu[k]; ``prev`` [slots, >= W] float32 (rows may be strided) holds every sequence's
+    last row and is moved on to the step's last."""
+    _need(out, "out"); _need(h, "h", out.dtype); _need(mu, "mu", out.dtype); _need(prev, "prev", torch.float32, contiguous=False)
+    n, W = h.shape
+    check(lib().ti_shift_blend(out.data_ptr(), h.data_ptr(), mu.data_ptr(), mu.shape[0], prev.data_ptr(), prev.stride(0), step.cu_seqlens.data_ptr(),
+                               step.seq_slots.data_ptr(), n, step.n_seqs, W, dtype_code(out.dtype), _stream()), "shift_blend")
+
+
+def decay_scan(o, rkv, r_off, k_off, v_off, dlog, w0, u, state, step, heads, dim):
+    """o_t = (S + diag(u) k v^T)^T r; S <- diag(exp(-exp(dlog_t + w0))) S + k v^T over the step's tokens of every sequence; ``state``
+    [slots, >= heads * dim * dim] float32 (rows may be strided); rkv [n, ld] with r, k, v from the given columns on; o, dlog float32."""
+    _need(o, "o", torch.float32); _need(rkv, "rkv", contiguous=False); _need(dlog, "dlog", torch.float32); _need(w0, "w0", torch.float32)
+    _need(u, "u", torch.float32); _need(state, "state", torch.float32, contiguous=False)
+    check(lib().ti_decay_scan(o.data_ptr(), rkv.data_ptr(), rkv.stride(0), r_off, k_off, v_off, dlog.data_ptr(), w0.data_ptr(), u.data_ptr(),
+                              state.data_ptr(), state.stride(0), step.cu_seqlens.data_ptr(), step.seq_slots.data_ptr(), rkv.shape[0], step.n_seqs,
+                              heads, dim, dtype_code(rkv.dtype), _stream()), "decay_scan")
+
+
+def delta_inputs(out, proj, conv, taps, hist, step, qk_heads, dim, value_channels, unit_eps):
+    """proj [n, 2 * qk_heads * dim + value_channels] -> causal convolution over time (history ``hist`` [slots, >= (taps - 1) * C]
+    float32), SiLU, unit q and k heads (q also times dim^-1/2) -> out float32."""
+    _need(out, "out", torch.float32); _need(proj, "proj", contiguous=False)
+    if hist is not None:
+        _need(hist, "hist", torch.float32, contiguous=False)
+    check(lib().ti_delta_inputs(out.data_ptr(), proj.data_ptr(), proj.stride(0), _ptr(conv), taps, _ptr(hist), hist.stride(0) if hist is not None else 0,
+                                step.cu_seqlens.data_ptr(), step.seq_slots.data_ptr(), proj.shape[0], step.n_seqs, qk_heads, dim, value_channels,
+                                unit_eps, dtype_code(proj.dtype), _stream()), "delta_inputs")
+
+
+def history_update(hist, proj, taps, step, channels):
+    """Every sequence's history [slots, >= (taps - 1) * channels] becomes its last taps - 1 rows of ``proj``."""
+    _need(hist, "hist", torch.float32, contiguous=False); _need(proj, "proj", contiguous=False)
+    check(lib().ti_history_update(hist.data_ptr(), hist.stride(0), proj.data_ptr(), proj.stride(0), taps, step.cu_seqlens.data_ptr(),
+                                  step.seq_slots.data_ptr(), step.n_seqs, channels, dtype_code(proj.dtype), _stream()), "history_update")
+
+
+def delta_scan(o, qkv, ba, a_log, dt_bias, state, step, heads, qk_heads, dim, vdim):
+    """The gated delta rule over the step's tokens of every sequence: S <- g S; e = beta (v - S^T k); S <- S + k e^T; o = S^T q with
+    beta = sigmoid(ba[:, h]), g = exp(-exp(a_log) softplus(ba[:, heads + h] + dt_bias)). qkv, ba, o float32."""
+    _need(o, "o", torch.float32); _need(qkv, "qkv", torch.float32); _need(ba, "ba", torch.float32); _need(a_log, "a_log", torch.float32)
+    _need(dt_bias, "dt_bias", torch.float32); _need(state, "state", torch.float32, contiguous=False)
+    check(lib().ti_delta_scan(o.data_ptr(), qkv.data_ptr(), qkv.stride(0), ba.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(),
+                              state.stride(0), step.cu_seqlens.data_ptr(), step.seq_slots.data_ptr(), qkv.shape[0], step.n_seqs, heads, qk_heads, dim,
+                              vdim, _stream()), "delta_scan")
+
+
+def heads_norm_gate(y, o, gate, w, eps, heads, vdim):
+    """y [n, heads * vdim] = o / rms(o over each head) * w * silu(gate); w [vdim] (shared by the heads) or [heads * vdim]."""
+    _need(y, "y"); _need(o, "o", torch.float32); _need(w, "w", y.dtype)
+    if gate is not None:
+        _need(gate, "gate", y.dtype, contiguous=False)
+    if w.numel() not in (vdim, heads * vdim):
+        raise KernelError(f"heads_norm_gate: a weight of {w.numel()} for {heads} heads of {vdim}")
+    check(lib().ti_heads_norm_gate(y.data_ptr(), o.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0, w.data_ptr(),
+                                   int(w.numel() == vdim), eps, y.shape[0], heads, vdim, dtype_code(y.dtype),
+                                   _stream()), "heads_norm_gate")
+
+
+def pair_combine(out, a, b, wa, wb, eps, scale_a, scale_b, dtype):
+    """out [n, size] float32 = scale_a * A' + scale_b * B'; with weights A' = A / rms(A) * wa (B likewise), else A' = A. A, B: rows of
+    ``dtype`` or float32 partial sums [s, n, size]."""
+    _need(out, "out", torch.float32)
+    n, size = out.shape
+    check(lib().ti_pair_combine(out.data_ptr(), *_rows_or_partials(a, dtype, "a"), *_rows_or_partials(b, dtype, "b"), _ptr(wa), _ptr(wb),
+                                int(wa is not None), eps, scale_a, scale_b, n, size, dtype_code(dtype), _stream()), "pair_combine")

@@ -2,6 +2,7 @@
 h = norm1(x), on a 32-bit stream.
 ``post_norm``: x += m norm1(mixer(x)); x += m norm2(ffn(x)); x += m token_input(x), on a 32-bit stream.
 ``sandwich``: x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x))), on a 32-bit stream.
+``hyper``: pre-norm sublayers that read, rewrite and write to several copies of a 32-bit stream through learned tables.
 
 Each residual add is fused with the norm that follows it, so a block receives the already
 normed input ``h`` and produces the next block's normed input with ``next_norm`` (the next
@@ -10,6 +11,10 @@ block's mixer norm, or the model's final norm), as AntoineBut/TileInfer.jl's ste
 """
 from __future__ import annotations
 
+import torch
+
+from ..config.spec import TensorDecl
+from ..kernels import ops
 from .base import register_block
 from .norm import StreamCast
 
@@ -125,4 +130,95 @@ class SandwichBlock:
         self.mixer_post_norm.branch_add(x, delta, 1.0, h, self.feed_forward_norm, bias=bias)
         delta = self.feed_forward.forward(h, step)
         self.feed_forward_post_norm.branch_add(x, delta, 1.0, h_out, next_norm)
+        return h_out
+
+
+class StreamsRead:
+    """Stands where a block's input norm would when the stream has several copies: h = norm(sum_s a[s] x_s) for x [n, S * size],
+    ``a`` the reader's blend (all ones: the sum of the copies, what the model's final norm reads)."""
+
+    def __init__(self, norm, blend, rt):
+        self.norm, self.blend = norm, [float(v) for v in blend]
+        self.blend_device = torch.tensor(self.blend, dtype=torch.float32, device=rt.device)
+
+    def read_args(self):
+        return self.norm.read_args()
+
+    def forward(self, x, out):
+        w, b, eps, centred = self.norm.read_args()
+        ops.streams_read_norm(out, x, self.blend_device, w, b, eps, centred)
+        return out
+
+
+@register_block("hyper")
+class HyperBlock:
+    """Pre-norm sublayers on S copies x_1 .. x_S of a 32-bit stream (hyper-connections). For sublayer q (the mixer, then the
+    feed-forward, which a layer may lack), with learned a_q [S], c_q [S] and M_q [S, S] (indexed [from, to]):
+
+        u = sum_s a_q[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s M_q[s, t] x_s + m c_q[t] y   for all t at once
+
+    m is the option ``residual_mult``. With ``streams`` 0 there is one stream and x += m sublayer(norm(x)): the same kernels with
+    S = 1, a = c = [1], M = [[1]]. Option ``tensors``: {1: {"in", "out", "mix"}, 2: {...}} names the learned tables. The kernel that
+    writes a sublayer's output back also makes the next reader's normed input, so the block receives h = norm_1(u) and leaves the next
+    block's (or the final norm's) input in ``h_out``; the norms are of a kind that offers ``read_args`` (``layernorm32``)."""
+
+    def __init__(self, spec, mixer, feed_forward, mixer_norm, feed_forward_norm, tensors=None, rt=None):
+        _no_out_bias(mixer, "hyper")
+        self.spec = spec
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        o = spec.options
+        self.mult = float(o.get("residual_mult", 1.0))
+        self.streams = S = max(1, int(o.get("streams") or 0))
+        self.tables = {}
+        for q in (1, 2):
+            if o.get("streams"):
+                names = o["tensors"][q]
+                get = lambda k: tensors[names[k]].detach().to("cpu", torch.float32)
+                a, c, M = get("in").flatten().tolist(), get("out").flatten().tolist(), get("mix").flatten().tolist()
+            else:
+                a, c, M = [1.0], [1.0], [1.0]
+            self.tables[q] = (a, [self.mult * v for v in c], M)
+        rt = rt if rt is not None else mixer.rt
+        self._read1 = StreamsRead(mixer_norm, self.tables[1][0], rt)
+        self._read2 = StreamsRead(feed_forward_norm, self.tables[2][0], rt) if feed_forward is not None else None
+
+    @classmethod
+    def tensors(cls, spec):
+        o = spec.options
+        S = int(o.get("streams") or 0)
+        out = []
+        if S:
+            for q in (1, 2):
+                if q == 2 and spec.feed_forward is None:
+                    continue
+                names = o["tensors"][q]
+                out += [TensorDecl(names["in"], (S,), ("const_plus_normal", 1.0 / S, 0.1), keep_dtype=True),
+                        TensorDecl(names["out"], (S,), ("const_plus_normal", 1.0, 0.2), keep_dtype=True),
+                        TensorDecl(names["mix"], (S, S), ("const_plus_normal", 1.0 / S, 0.15), keep_dtype=True)]
+        return out
+
+    @property
+    def input_norm(self):
+        return self._read1
+
+    def _next(self, nxt):
+        """(blend, norm arguments) of whoever reads the stream next: another reader of copies, or a norm that reads their sum."""
+        if isinstance(nxt, StreamsRead):
+            return nxt.blend, nxt.read_args()
+        return [1.0] * self.streams, nxt.read_args()
+
+    def forward(self, x, h, step, cache, next_norm, h_out):
+        a1, c1, M1 = self.tables[1]
+        delta = self.mixer.forward(h, step, cache)
+        if self.feed_forward is None:
+            blend, (w, b, eps, centred) = self._next(next_norm)
+            ops.streams_update(x, delta, M1, c1, blend, h_out, w, b, eps, centred)
+            return h_out
+        w, b, eps, centred = self._read2.read_args()
+        ops.streams_update(x, delta, M1, c1, self._read2.blend, h, w, b, eps, centred)
+        a2, c2, M2 = self.tables[2]
+        delta = self.feed_forward.forward(h, step)
+        blend, (w, b, eps, centred) = self._next(next_norm)
+        ops.streams_update(x, delta, M2, c2, blend, h_out, w, b, eps, centred)
         return h_out

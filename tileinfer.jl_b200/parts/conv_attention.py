@@ -21,12 +21,22 @@ tensors and reads the pages of an earlier layer, with queries, convolution state
 Keys and values of different sizes share the paged attention kernels by filling both up to one row length ``padded`` with zeros
 (a zero adds nothing to a score, and the outputs beyond value_dim are dropped by the gate's kernel).
 
+Further options. ``norm_weight`` False: the norms of q and k have no weight (every head is only divided by its root mean square).
+``gate`` "head": W_g has one row per head and the whole head is multiplied by that one sigmoid. ``chunk`` c: a key is visible only
+inside the query's chunk of c positions, floor(i / c) = floor(j / c), counted from the sequence's start. ``distance_bias`` far: a
+learned table ``rel`` [rows, heads] adds rel[bucket(i - j), head] to the scaled score, bucket(n) = n for n < rows / 2 and
+min(rows - 1, rows / 2 + floor(ln(n / (rows / 2)) / ln(far / (rows / 2)) * (rows - rows / 2))) beyond: one row per small distance,
+logarithmic steps up to ``far``, the last row from there on. Attention with a chunk or a distance bias runs in the plain paged kernel
+in every element type.
+
 Record: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``, ``window``, ``kv_source``, ``qk_norm_eps`` and the options
-``value_dim``, ``conv_taps`` (0: none), ``bias``, ``out_bias``, ``row_norm``, ``head_norm``, ``sink``, ``gate``.
+``value_dim``, ``conv_taps`` (0: none), ``bias``, ``out_bias``, ``row_norm``, ``head_norm``, ``norm_weight``, ``sink``, ``gate``,
+``chunk``, ``distance_bias``.
 """
 from __future__ import annotations
 
 import dataclasses
+import math
 
 import torch
 
@@ -34,6 +44,18 @@ from ..config.spec import MixerSpec, TensorDecl
 from ..kernels import ops
 from .base import CacheRequest, Mixer, register_mixer
 from .linear import Linear
+
+
+def distance_buckets(rows: int, far: float, count: int):
+    """bucket(n) for n = 0 .. count - 1 (see the module's text); from n = far on it is rows - 1."""
+    half = rows // 2
+    out = []
+    for n in range(count):
+        if n < half or half == 0:
+            out.append(min(n, rows - 1))
+        else:
+            out.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+    return out
 
 
 def _flags(o):
@@ -64,9 +86,25 @@ class ConvAttention(Mixer):
         self.bias = torch.cat([get(n[k] + n["bias_suffix"]) for k in kinds]).contiguous() if self.bias_on else None
         self.conv = torch.cat([get(n[k] + n["conv_suffix"]) for k in kinds], 0).contiguous() if self.taps else None
         self.head_norm = bool(o.get("head_norm", False))
+        self.gate_per_head = o.get("gate") == "head"
         self.out_bias = get(n["o"] + n["bias_suffix"]) if o.get("out_bias", False) else None
-        self.q_norm = get(n["q"] + n["norm_suffix"]) if self.row_norm else None
-        self.k_norm = get(n["k"] + n["norm_suffix"]) if self.row_norm and self.own_kv else None
+        if self.row_norm and not o.get("norm_weight", True):
+            # A norm without a weight: the kernels' weighted norm with ones.
+            size = self.dim if self.head_norm else None
+            ones = lambda rows: torch.ones(size or rows, dtype=rt.dtype, device=rt.device)
+            self.q_norm, self.k_norm = ones(self.nq * self.dim), (ones(self.nkv * self.dim) if self.own_kv else None)
+        else:
+            self.q_norm = get(n["q"] + n["norm_suffix"]) if self.row_norm else None
+            self.k_norm = get(n["k"] + n["norm_suffix"]) if self.row_norm and self.own_kv else None
+        self.chunk = int(o.get("chunk") or 0)
+        self.distance_bias = None
+        if o.get("distance_bias"):
+            rel = rt.param(tensors[p + n["rel"]], keep_dtype=True).float()           # [rows, heads]
+            far = float(o["distance_bias"])
+            count = int(math.ceil(far)) + 1                                            # from `far` on every distance has the last row
+            index = torch.tensor(distance_buckets(rel.shape[0], far, count), dtype=torch.long, device=rel.device)
+            self.distance_bias = rel[index].t().contiguous()                          # [heads, count]: the bias by distance
+        self.out_name, self.gated_name = "mixer.delta", "conv_attention.gated"
         self.sink = rt.param(tensors[p + n["sink"]], keep_dtype=True).float().contiguous() if self.sink_on else None
         self.o = Linear(get(n["o"]), rt, "o")
         self.o.partials_name = "mixer.partials"
@@ -93,12 +131,14 @@ class ConvAttention(Mixer):
                 out.append(TensorDecl(p + n[k] + n["bias_suffix"], (r,), ("normal", 0.1)))
             if taps:
                 out.append(TensorDecl(p + n[k] + n["conv_suffix"], (r, taps), ("const_plus_normal", 1.0 / taps, 0.3)))
-            if row_norm and k != "v":
+            if row_norm and k != "v" and o.get("norm_weight", True):
                 out.append(TensorDecl(p + n[k] + n["norm_suffix"], (D if o.get("head_norm", False) else r,), ("one_plus_normal", 0.1)))
         if sink:
             out.append(TensorDecl(p + n["sink"], (H,), ("normal", 1.0), keep_dtype=True))
         if gate:
-            out.append(TensorDecl(p + n["g"], (H * V, W), std(W)))
+            out.append(TensorDecl(p + n["g"], (H if o.get("gate") == "head" else H * V, W), std(W)))
+        if o.get("distance_bias"):
+            out.append(TensorDecl(p + n["rel"], (int(o.get("distance_rows", 16)), H), ("normal", 1.0), keep_dtype=True, free_dims=(0,)))
         return out
 
     def cache_request(self):
@@ -110,7 +150,7 @@ class ConvAttention(Mixer):
         return tuple(out)
 
     def decode_plan(self, group):
-        if not (self.rt.fast and self.rt.dtype == torch.bfloat16) or not self.own_kv:
+        if not (self.rt.fast and self.rt.dtype == torch.bfloat16) or not self.own_kv or self.chunk or self.distance_bias is not None:
             return None
         from ..kernels import fast
         return fast.SplitKvPlan(self.nkv, group.page_size, group.num_pages * group.page_size)
@@ -130,16 +170,16 @@ class ConvAttention(Mixer):
             ops.conv_state_update(cache.state, rows, self.bias, self.taps, step, C)
         attn = rt.buffer("attention.out", (n, nq * Dp))
         done = False
-        if rt.fast:
+        if rt.fast and not self.chunk and self.distance_bias is None:
             from ..kernels import fast
             done = fast.attention(attn, q, cache, meta, step, self.attn_spec, sink=self.sink)
         if not done:
             ops.attention_plain(attn, q, cache.k, cache.v, meta.block_table, step.tok_slot, step.positions, s.scale, nq, nkv, Dp,
-                                cache.page_size, window=s.window or 0, sink=self.sink)
+                                cache.page_size, window=s.window or 0, sink=self.sink, chunk=self.chunk, distance_bias=self.distance_bias)
         if self.gated or Dp != V:
-            y = rt.buffer("conv_attention.gated", (n, nq * V))
-            ops.sigmoid_gate(y, attn, rows[:, C:] if self.gated else None, nq, V, Dp)
+            y = rt.buffer(self.gated_name, (n, nq * V))
+            ops.sigmoid_gate(y, attn, rows[:, C:] if self.gated else None, nq, V, Dp, per_head=self.gate_per_head)
         else:
             y = attn                                # no gate and no filling to drop: the heads' outputs as they are
-        out = rt.buffer("mixer.delta", (n, s.hidden_size))
+        out = rt.buffer(self.out_name, (n, s.hidden_size))
         return self.o.forward(y, out, allow_partials=True)

@@ -85,6 +85,41 @@ class LayerNorm32(RMSNorm32):
     def __init__(self, spec: NormSpec, tensors, rt):
         super().__init__(spec, tensors, rt)
         self.offset = ops.NORM_CENTRED | (ops.NORM_OFFSET if spec.options.get("offset", False) else 0)
+        # Option ``bias``: y + b, with b the tensor of the weight's name plus ``bias_suffix``. Only the kernels that read several copies
+        # of the stream (``streams_read_norm``, ``streams_update``) take a bias; the blocks written for them ask for ``read_args``.
+        self.bias = rt.param(tensors[spec.weight_name + spec.options.get("bias_suffix", ".b")]) if spec.options.get("bias") else None
+
+    @classmethod
+    def tensors(cls, spec: NormSpec):
+        out = super().tensors(spec)
+        if spec.options.get("bias"):
+            out.append(TensorDecl(spec.weight_name + spec.options.get("bias_suffix", ".b"), (spec.size,), ("normal", spec.options.get("init_std", 0.02))))
+        return out
+
+    def read_args(self):
+        """(weight, bias or None, eps, centred) for the kernels that norm a blend of the stream's copies."""
+        if self.offset & ops.NORM_OFFSET:
+            raise NotImplementedError("a gain stored minus one is not built for the kernels that read several copies of the stream")
+        return (self.weight, self.bias, self.eps, True)
+
+    def _no_bias(self, what):
+        if self.bias is not None:
+            raise NotImplementedError(f"layernorm32 with a bias does not serve {what}")
+
+    def forward(self, x, out):
+        if self.bias is None:
+            return super().forward(x, out)
+        ones = self.rt.ones1()
+        ops.streams_read_norm(out, x, ones, self.weight, self.bias, self.eps, True)
+        return out
+
+    def out_args(self):
+        self._no_bias("as the next norm of branch_add")
+        return super().out_args()
+
+    def branch_add(self, *a, **k):
+        self._no_bias("branch_add")
+        return super().branch_add(*a, **k)
 
     def sum_add(self, x, d1, d2, out):
         raise NotImplementedError("layernorm32 does not serve blocks that add two sublayers' outputs at once")

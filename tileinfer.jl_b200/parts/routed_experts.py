@@ -6,6 +6,9 @@ every token and is added.
     out = sum_chosen unit_e(score_e * h)  [+ unit_shared(h)]         with ``scale_input`` (the score scales the INPUT)
     out = sum_chosen score_e * unit_e(h)  [+ unit_shared(h)]         without it
 
+With ``gated`` False a unit has no gate matrix: unit(u) = Wdown act(Wup u), ``activation`` "relu2" (max(z, 0)^2), no clamp and no
+shared unit.
+
 Options of the record: ``experts``, ``top``, ``limit`` (None: no clamp), ``sigmoid_slope``, ``up_shift``, ``scale_input``,
 ``shared_size`` / ``shared_limit`` (0: no shared unit). ``intermediate_size`` is an expert's size. A router with more rules
 (any of the following options) is chosen by ``csrc/routed_experts.cu``'s ``router_select``:
@@ -50,6 +53,9 @@ class RoutedExperts(FeedForward):
         self.slope, self.shift = float(o.get("sigmoid_slope", 1.0)), float(o.get("up_shift", 0.0))
         self.scale_input = bool(o.get("scale_input", False))
         get = lambda name: rt.param(tensors[p + name])
+        self.gated = bool(o.get("gated", True))
+        if not self.gated and (o.get("activation") != "relu2" or int(o.get("shared_size", 0)) or o.get("limit") is not None):
+            raise ValueError("routed_experts: a unit without a gate has the activation relu2, no clamp and no shared unit")
         self.select = _has_rules(o)
         self.softmax, self.renormalize = o.get("score", "sigmoid") == "softmax", bool(o.get("renormalize", False))
         self.pass_through = int(o.get("pass_through", 0))
@@ -70,7 +76,7 @@ class RoutedExperts(FeedForward):
         units = [p + n["expert"].format(e) for e in range(self.experts)]
         unit = lambda u, k: rt.param(tensors[u + n[k]])
         F, W = spec.intermediate_size, spec.hidden_size
-        gate_up = [torch.cat([unit(u, "gate"), unit(u, "up")], 0) for u in units]
+        gate_up = [torch.cat([unit(u, "gate"), unit(u, "up")], 0) if self.gated else unit(u, "up") for u in units]
         down = [unit(u, "down") for u in units]
         limits = [self.limit] * self.experts
         shared_limit = float(o["shared_limit"]) if o.get("shared_limit") is not None else float("inf")
@@ -110,8 +116,8 @@ class RoutedExperts(FeedForward):
             out.append(TensorDecl(p + n["shared_gate"], (1, W), std(W)))
 
         def unit(u, size):
-            return [TensorDecl(u + n["gate"], (size, W), std(W)), TensorDecl(u + n["up"], (size, W), std(W)),
-                    TensorDecl(u + n["down"], (W, size), std(size))]
+            gate = [TensorDecl(u + n["gate"], (size, W), std(W))] if o.get("gated", True) else []
+            return gate + [TensorDecl(u + n["up"], (size, W), std(W)), TensorDecl(u + n["down"], (W, size), std(size))]
         for e in range(int(o["experts"])):
             out += unit(p + n["expert"].format(e), F)
         if int(o.get("shared_size", 0)):
@@ -148,8 +154,12 @@ class RoutedExperts(FeedForward):
         ops.expert_plan(ids, self.units, tile, pair_row, row_pair, plan)
         ops.expert_gather(xs, h, pair_row, scores, per_token, self.scale_input)
         act = rt.buffer("experts.act", (rows, F))
-        gu = rt.buffer("experts.gate_up", (rows, 2 * F))
-        if fast is not None and fast.grouped_linear(gu, xs, self.gate_up, plan, tile):
+        gu = rt.buffer("experts.gate_up", (rows, 2 * F if self.gated else F))
+        if not self.gated:
+            if not (fast is not None and fast.grouped_linear(gu, xs, self.gate_up, plan, tile)):
+                ops.grouped_gemm(gu, xs, self.gate_up, plan, tile)
+            ops.relu2(act, gu)
+        elif fast is not None and fast.grouped_linear(gu, xs, self.gate_up, plan, tile):
             ops.gated_unit_limit(act, gu, 0.0, self.slope, self.shift, plan=plan, tile=tile, limits=self.limits)
         else:
             ops.grouped_gemm(act, xs, self.gate_up, plan, tile, gated=True, limits=self.limits, slope=self.slope, shift=self.shift)

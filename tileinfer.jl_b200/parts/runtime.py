@@ -54,6 +54,12 @@ class Runtime:
         view = self._views[key] = buf[:count].view(*shape)
         return view
 
+    def ones1(self) -> torch.Tensor:
+        """[1.0] float32 on the device (the blend of a stream that has one copy)."""
+        if getattr(self, "_ones1", None) is None:
+            self._ones1 = torch.ones(1, dtype=torch.float32, device=self.device)
+        return self._ones1
+
     def param(self, t: torch.Tensor, keep_dtype: bool = False) -> torch.Tensor:
         """A checkpoint tensor on the device, in the element type the kernels compute with."""
         t = t.to(self.device)

@@ -66,6 +66,8 @@ def load_tensors(model_dir: str, decls: Sequence[TensorDecl], ignorable: Iterabl
         ok = shape == want
         if not ok and d.allow_extra_rows and len(shape) == len(want) and shape[1:] == want[1:] and shape[0] >= want[0]:
             ok = True
+        if not ok and d.free_dims and len(shape) == len(want) and all(a == b or i in d.free_dims for i, (a, b) in enumerate(zip(shape, want))):
+            ok = min(shape) >= 1
         if not ok and _numel(shape) == 1 and _numel(want) == 1:
             ok = True          # a scalar may be stored as [] or [1]
         if not ok:
