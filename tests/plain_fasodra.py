@@ -144,7 +144,7 @@ def short_conv(x, taps_w):
 def gated_delta(h, w, p, m, eps):
     """The gated delta rule: the state forgets by a decay per head, and a write replaces what the key already reads out."""
     t = h.shape[0]
-    H, G, D, V = m["heads"], m.get("kv_heads") or m["heads"], m["dim"], m["vdim"]
+    H, G, D, V = m["heads"], m.get("kv_heads") or m["heads"], m["dim"], m.get("vdim") or m["dim"]
     silu = torch.nn.functional.silu
     proj = lambda name: silu(short_conv(h @ w[p + name].T, w[p + name + ".conv"])) if (p + name + ".conv") in w else silu(h @ w[p + name].T)
     q, k, v = _heads(proj("q"), G), _heads(proj("k"), G), _heads(proj("v"), H)
@@ -186,16 +186,18 @@ def router_scores(h, w, p):
     return torch.softmax(h @ w[p + "router"].T, -1)
 
 
-def routed_experts(h, w, p, f, margins=None):
-    """Every token's ``top`` experts by softmax score, their scores divided by their sum; an expert is down(max(up x, 0)^2)."""
+def routed_experts(h, w, p, f, margins=None, forced=None):
+    """Every token's ``top`` experts by softmax score, their scores divided by their sum; an expert is down(max(up x, 0)^2).
+    ``forced`` {position: experts}: choices made elsewhere, taken as they are (the weights are still this function's scores)."""
     experts, top = f["router"]["experts"], f["router"]["top"]
     s = router_scores(h, w, p)
     out = torch.zeros_like(h)
     for i in range(h.shape[0]):
         order = sorted(range(experts), key=lambda e: (-float(s[i, e]), e))
-        chosen = order[:top]
+        chosen = order[:top] if forced is None else list(forced[i])
         if margins is not None:
-            margins.append(float(s[i, order[top - 1]] - s[i, order[top]]) if top < experts else float("inf"))
+            # how far, in logits, the last chosen expert is ahead of the best one left out
+            margins.append(float(torch.log(s[i, order[top - 1]]) - torch.log(s[i, order[top]])) if top < experts else float("inf"))
         total = sum(s[i, e] for e in chosen) + 1e-20
         for e in chosen:
             a = torch.relu(w[f"{p}e{e}.up"] @ h[i]) ** 2
@@ -204,9 +206,10 @@ def routed_experts(h, w, p, f, margins=None):
 
 
 # ---------------------------------------------------------------- the model
-def forward(config, weights, tokens, dtype=torch.float64, layers_out=None, margins=None):
+def forward(config, weights, tokens, dtype=torch.float64, layers_out=None, margins=None, forced=None):
     """Logits [len(tokens), vocab] of one request; ``layers_out``: a list that receives the stream after every layer (the sum
-    of the streams, where there are several); ``margins``: a list that receives one list of router margins per layer."""
+    of the streams, where there are several); ``margins``: a list that receives one list of router margins per layer; ``forced``
+    {layer: {position: experts}}: router choices to take instead of this implementation's own."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
     mult = float(config.get("residual_mult", 1.0))
@@ -221,7 +224,7 @@ def forward(config, weights, tokens, dtype=torch.float64, layers_out=None, margi
             mg = [] if margins is not None else None
             if margins is not None:
                 margins.append(mg)
-            subs.append((2, lambda hh, mg=mg: routed_experts(hh, w, p + "mlp.", layer["mlp"], mg)))
+            subs.append((2, lambda hh, mg=mg: routed_experts(hh, w, p + "mlp.", layer["mlp"], mg, None if forced is None else forced[i])))
         elif margins is not None:
             margins.append([])
         for qn, fn in subs:

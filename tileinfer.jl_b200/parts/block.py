@@ -171,7 +171,7 @@ class HyperBlock:
         self.mult = float(o.get("residual_mult", 1.0))
         self.streams = S = max(1, int(o.get("streams") or 0))
         self.tables = {}
-        for q in (1, 2):
+        for q in (1, 2) if feed_forward is not None else (1,):
             if o.get("streams"):
                 names = o["tensors"][q]
                 get = lambda k: tensors[names[k]].detach().to("cpu", torch.float32)

@@ -101,6 +101,9 @@ class ConvAttention(Mixer):
         if o.get("distance_bias"):
             rel = rt.param(tensors[p + n["rel"]], keep_dtype=True).float()           # [rows, heads]
             far = float(o["distance_bias"])
+            if far <= rel.shape[0] // 2:
+                raise ValueError(f"conv_attention: a bias table of {rel.shape[0]} rows has a row per distance below {rel.shape[0] // 2}, "
+                                 f"which its farthest distance {far} must exceed")
             count = int(math.ceil(far)) + 1                                            # from `far` on every distance has the last row
             index = torch.tensor(distance_buckets(rel.shape[0], far, count), dtype=torch.long, device=rel.device)
             self.distance_bias = rel[index].t().contiguous()                          # [heads, count]: the bias by distance
