@@ -7,6 +7,7 @@ model with random weights (bfloat16), plus prefill throughput and roofline fract
     python bench.py --preset vogilix [--timeline]  (the Vogilix design at two sizes beside Apertus layers of equal size)
     python bench.py --preset zudepel [--timeline]  (the Zudepel design at two sizes beside Vogilix layers of equal size)
     python bench.py --preset sozanex [--timeline]  (the Sozanex design at two sizes beside Vogilix layers of equal size)
+    python bench.py --preset fasodra [--timeline]  (the Fasodra design at two sizes beside Zudepel layers of equal size)
 
 Prints one JSON line. A "step" is one decode step of the whole batch (default batch 8, every
 sequence after 1,023 cached positions, context 4,096). ``value`` is decoded tokens per second
@@ -610,6 +611,82 @@ def run_sozanex(args, pk, pk_source):
     return 0
 
 
+def fasodra_config(size: str, layers: int):
+    """Layers of a real model's sizes: chunked attention with a distance bias, the pair of attention and the gated delta rule, and
+    the pair of gated attention and time mixing, in turn; every layer with routed squared-rectifier experts; two copies of the
+    stream."""
+    w, heads, kv_heads, dim, experts, top, ff, vocab, chunk = {
+        "mid": (2048, 16, 4, 128, 32, 4, 1024, 32768, 1024),
+        "wide": (4096, 32, 8, 128, 64, 6, 1408, 65536, 2048)}[size]
+    moe = {"expert": {"ff": ff}, "kind": "moe", "router": {"experts": experts, "top": top}}
+    left = {"dim": dim, "heads": heads, "kv_heads": kv_heads, "rot": {"base": 10000.0, "dims": dim // 2}, "scale": dim ** -0.5, "vdim": dim}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            m = {"bias_max": 2 * chunk, "dim": dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": chunk}, "scale": dim ** -0.5, "vdim": dim}
+            out.append({"mixer": m, "mlp": moe, "type": "attention"})
+        elif i % 4 == 1:
+            right = {"conv": 4, "dim": dim, "heads": heads, "kv_heads": heads // 2, "vdim": dim}
+            out.append({"mixer": {"left": dict(left), "right": right}, "mlp": moe, "type": "parallel_2"})
+        else:
+            right = {"dim": 64, "heads": w // 64}
+            out.append({"mixer": {"left": dict(left), "left_scale": 1.0, "right": right, "right_scale": 1.0}, "mlp": moe, "type": "parallel"})
+    return {"architecture": "Fasodra", "vocab": vocab, "width": w, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "streams": 2, "layers": out}
+
+
+def run_fasodra(args, pk, pk_source):
+    """Prefill and decode throughput of the Fasodra design at two sizes, each beside Zudepel layers of the same width, depth, heads,
+    experts and expert sizes (the library's closest model: a recurrence over a matrix state beside attention, routed experts, a
+    32-bit stream); with --timeline also the per-kernel device times of one prompt step and one decode step of both (stderr)."""
+    import torch
+    from tileinfer_b200.config import config_from_dict
+    from tileinfer_b200.engine import Engine
+    layers = args.layers or 8
+    steps, warmup = max(8, min(args.steps, 32)), max(args.warmup, 3)
+    clocks = ClockSampler()
+    clocks.start()
+    out = []
+    for size in ("mid", "wide"):
+        for name, raw in (("fasodra", fasodra_config(size, layers)), ("zudepel", zudepel_config(size, layers))):
+            cfg = config_from_dict(raw)
+            engine = Engine.random(cfg, seed=0, dtype=args.dtype, max_context=4096, max_seqs=64, max_tokens=64 * 1280,
+                                   max_step_tokens=8192)
+            row = {"size": size, "model": name, "layers": layers, "weights_gb": round(engine.weight_bytes() / 1e9, 3),
+                   "cache_bytes_per_position": engine.kv_bytes_per_position()}
+            for tokens in (512, 2048):
+                ms = time_prefill(engine, tokens, cfg.vocab_size, reps=3)
+                row[f"prefill_{tokens}_ms"] = round(ms, 3)
+                row[f"prefill_{tokens}_tok_s"] = round(tokens * 1000.0 / ms, 1)
+            for b in (1, 8, 64):
+                ms, _, launches = time_decode(engine, b, steps, warmup, cfg.vocab_size, count_launches=True)
+                row[f"decode_b{b}_ms"] = round(ms, 4)
+                row[f"decode_b{b}_tok_s"] = round(b * 1000.0 / ms, 1)
+                row[f"decode_b{b}_launches"] = launches
+            engine.check_health()
+            out.append(row)
+            del engine
+            torch.cuda.empty_cache()
+    clock_info = clocks.stop()
+    if args.timeline:
+        from tileinfer_b200.kernels import microbench
+        import contextlib
+        with contextlib.redirect_stdout(sys.stderr):
+            for size in ("mid", "wide"):
+                for name, raw in (("fasodra", fasodra_config(size, 4)), ("zudepel", zudepel_config(size, 4))):
+                    cfg = config_from_dict(raw)
+                    print(f"--- {size} {name}: prompt of 2,048 tokens")
+                    microbench.timeline(1, 0, prefill_tokens=2048, config=cfg, first=90 if name == "fasodra" else 1)
+                    for b in (8, 64):
+                        print(f"--- {size} {name}: decode step of batch {b}")
+                        microbench.timeline(b, 0, config=cfg, first=90 if (b == 8 and name == "fasodra") else 1)
+    print(json.dumps({"metric": "prefill and decode of the Fasodra design beside Zudepel layers of equal size", "n_gpus": 1,
+                      "steps": steps, "warmup": warmup, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+                      "data": "synthetic: random weights, uniform random token ids",
+                      "config": {"cached_positions": CACHED, "peaks": pk_source, "l2": "every step reads more weights than L2 holds"},
+                      "clocks": clock_info, "rows": out}))
+    return 0
+
+
 def flops_prefill(cfg, n_layers, tokens):
     H, I, D = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
@@ -638,7 +715,7 @@ def main(argv=None) -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick checks)")
     ap.add_argument("--timeline", action="store_true", help="--preset vogilix: per-kernel device times of its steps, on stderr")
-    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b", "sweep", "vogilix", "zudepel", "sozanex"],
+    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b", "sweep", "vogilix", "zudepel", "sozanex", "fasodra"],
                     help="8b: the headline line (default); 8b-long: 8 unequal sequences of up to 32,768 positions; "
                          "70b: Apertus-70B sizes, 141 GB of weights")
     args = ap.parse_args(argv)
@@ -664,6 +741,8 @@ def main(argv=None) -> int:
         return run_sweep(args, *peaks())
     if args.preset == "vogilix":
         return run_vogilix(args, *peaks())
+    if args.preset == "fasodra":
+        return run_fasodra(args, pk, pk_source)
     if args.preset == "sozanex":
         return run_sozanex(args, *peaks())
     if args.preset == "zudepel":

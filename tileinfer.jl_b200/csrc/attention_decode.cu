@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
     bf16* __restrict__ out, const bf16* q, const bf16* k_cache, const bf16* v_cache,
     const int* block_table, int table_stride, const int* seq_slots,
     const int* kv_lens, const int* work, float* __restrict__ ws_o, float* __restrict__ ws_ml, float scale_log2e, int nq,
-    int nkv, int splits, int window, const float* __restrict__ sink) {
+    int nkv, int splits, int window, const float* __restrict__ sink, AttnExtras ex) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     typedef DecodeSmem<D> SM;
     constexpr int KS = D / 16, NT = D / 8;
@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
     // The step's lengths and block tables were uploaded before its first kernel, and every page but
     // the sequence's last one holds only older positions: their copies start BEFORE waiting for the
     // kernel that writes this step's key, value and query.
-    const int first_key = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    int first_key = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    if (ex.chunk > 0 && kv_len > 0) first_key = max(first_key, ((kv_len - 1) / ex.chunk) * ex.chunk);       // the chunk of the step's token
     const int t_begin = first_key / AD_PAGE, t_end = (kv_len + AD_PAGE - 1) / AD_PAGE;
     const int n_tiles = t_end - t_begin;
     const int my_lo = t_begin + (int)((long long)n_tiles * split / parts);
@@ -116,6 +117,10 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;       // rows g and g + 8
+    // The rows of the distance bias for this thread's two query heads (rows beyond the group read the first head's: unused).
+    const int head0 = kvh * full_group + slab * 16;
+    const float* bias0 = ex.bias != nullptr ? ex.bias + (size_t)(head0 + (g < group ? g : 0)) * ex.bias_len : nullptr;
+    const float* bias1 = ex.bias != nullptr ? ex.bias + (size_t)(head0 + (g + 8 < group ? g + 8 : 0)) * ex.bias_len : nullptr;
 
     for (int tile = my_lo; tile < my_hi; ++tile) {
         const int stage = (tile - my_lo) % SM::STAGES;
@@ -126,7 +131,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
         const bf16* kt = tiles + (size_t)stage * 2 * SM::TILE;
         const bf16* vt = kt + SM::TILE;
 
-        decode_tile<D>(kt, vt, qf, o, m0, m1, l0, l1, tile, warp, lane, kv_len, first_key, scale_log2e);
+        decode_tile<D>(kt, vt, qf, o, m0, m1, l0, l1, tile, warp, lane, kv_len, first_key, scale_log2e, bias0, bias1, ex.bias_len);
     }
     cp_async_wait<0>();
     __syncthreads();
@@ -238,7 +243,7 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws
 template <int D>
 static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v, const int* table, int table_stride,
                          const int* seq_slots, const int* kv_lens, const int* work, const int* seq_work, float* ws_o, float* ws_ml,
-                         float scale, int B, int nq, int nkv, int splits, int window, const float* sink, cudaStream_t stream) {
+                         float scale, int B, int nq, int nkv, int splits, int window, const float* sink, AttnExtras ex, cudaStream_t stream) {
     static bool configured = false;
     const size_t smem = DecodeSmem<D>::BYTES > (size_t)AD_WARPS * 16 * (D + 2) * 4 ? DecodeSmem<D>::BYTES
                                                                                     : (size_t)AD_WARPS * 16 * (D + 2) * 4;
@@ -251,10 +256,10 @@ static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v,
     const int slabs = (nq / nkv + 15) / 16;
     if (work != nullptr && splits > 1)
         ti_launch(attention_decode_kernel<D, true>, dim3(B * splits, nkv * slabs), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
-                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window, sink);
+                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window, sink, ex);
     else
         ti_launch(attention_decode_kernel<D, false>, dim3(splits, nkv * slabs, B), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
-                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window, sink);
+                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window, sink, ex);
     if (int rc = ti_check_launch("attention_decode")) return rc;
     if (splits > 1) {
         ti_launch(attention_combine_kernel, dim3(B * nq), dim3(D <= 64 ? 64 : 128), 0, stream, out, ws_o, ws_ml, seq_work, D, nq, splits, sink);
@@ -270,11 +275,15 @@ static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v,
 // part << 8 | parts (at most 32), or -1 for a slot left without work; the sequence's length), 8-byte aligned
 // pairs; seq_work[sequence] = first slot << 8 | parts; a sequence's slots are consecutive. Without them every sequence takes `splits` equal parts.
 // `sink` [nq] float (or null): one more term exp(sink[head]) in every softmax's denominator, with no key and no value.
-extern "C" int ti_attention_decode_sink(void* out, const void* q, const void* k_cache, const void* v_cache,
-                                        const int* block_table, int table_stride, const int* seq_slots, const int* kv_lens,
-                                        const int* work, const int* seq_work, float* ws_o, float* ws_ml, float scale, int B,
-                                        int nq, int nkv, int D, int page_size, int splits, int window, const float* sink, cudaStream_t stream) {
+// `chunk`, `dist_bias` [nq][bias_len] (times log2 e), `bias_len`: see AttnExtras.
+extern "C" int ti_attention_decode_biased(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                          const int* block_table, int table_stride, const int* seq_slots, const int* kv_lens,
+                                          const int* work, const int* seq_work, float* ws_o, float* ws_ml, float scale, int B,
+                                          int nq, int nkv, int D, int page_size, int splits, int window, const float* sink, int chunk,
+                                          const float* dist_bias, int bias_len, cudaStream_t stream) {
     if (B == 0) return 0;
+    TI_REQUIRE(chunk >= 0 && (dist_bias == nullptr || bias_len > 0), "attention_decode: chunk %d, bias table of %d", chunk, bias_len);
+    const AttnExtras ex = {chunk, dist_bias, bias_len};
     if (page_size != AD_PAGE || nq % nkv != 0 || nq / nkv > 128 || D % 16 != 0 || B > 32767 || (long long)nkv * ((nq / nkv + 15) / 16) > 65535) {
         ti_fail("attention_decode takes page size %d, at most 128 query heads per KV head and head sizes in steps of 16; "
                 "got page %d, %d/%d heads, head size %d", AD_PAGE, page_size, nq, nkv, D);
@@ -287,7 +296,7 @@ extern "C" int ti_attention_decode_sink(void* out, const void* q, const void* k_
 #define AD_CASE(d)                                                                                                     \
     case d:                                                                                                            \
         return launch_decode<d>((bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,     \
-                                table_stride, seq_slots, kv_lens, work, seq_work, ws_o, ws_ml, scale, B, nq, nkv, splits, window, sink, stream);
+                                table_stride, seq_slots, kv_lens, work, seq_work, ws_o, ws_ml, scale, B, nq, nkv, splits, window, sink, ex, stream);
     switch (D) {
         AD_CASE(16) AD_CASE(32) AD_CASE(48) AD_CASE(64) AD_CASE(80) AD_CASE(96) AD_CASE(112) AD_CASE(128) AD_CASE(256)
         default:
@@ -295,6 +304,14 @@ extern "C" int ti_attention_decode_sink(void* out, const void* q, const void* k_
             return 2;
     }
 #undef AD_CASE
+}
+
+extern "C" int ti_attention_decode_sink(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                        const int* block_table, int table_stride, const int* seq_slots, const int* kv_lens,
+                                        const int* work, const int* seq_work, float* ws_o, float* ws_ml, float scale, int B,
+                                        int nq, int nkv, int D, int page_size, int splits, int window, const float* sink, cudaStream_t stream) {
+    return ti_attention_decode_biased(out, q, k_cache, v_cache, block_table, table_stride, seq_slots, kv_lens, work, seq_work, ws_o, ws_ml, scale,
+                                      B, nq, nkv, D, page_size, splits, window, sink, 0, nullptr, 0, stream);
 }
 
 extern "C" int ti_attention_decode_shared(void* out, const void* q, const void* k_cache, const void* v_cache,

@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
     bf16* __restrict__ out, const bf16* q, const bf16* k_cache, const bf16* v_cache,
     const int* block_table, int table_stride, const int* seq_slots,
     const int* cu_seqlens, const int* kv_lens, int n_seqs, float scale_log2e, int nq, int nkv,
-    int tokens_per_tile, int window, const float* __restrict__ sink) {
+    int tokens_per_tile, int window, const float* __restrict__ sink, AttnExtras ex) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     typedef PrefillSmem<D> SM;
     constexpr int CPR = D / 8, KS = D / 16, NT = D / 8;
@@ -78,8 +78,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
     const int tok0 = r0 / group, tok1 = r1 / group;
     const bool live0 = tok0 < n_tok, live1 = tok1 < n_tok;
     const int pos0 = live0 ? start + j0 + tok0 : -1, pos1 = live1 ? start + j0 + tok1 : -1;
-    const int lo0 = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
-    const int lo1 = (window > 0 && pos1 + 1 > window) ? pos1 + 1 - window : 0;
+    // The first key a position sees: the window's, and with chunks the first of the position's chunk.
+    auto first_seen = [&](int pos) {
+        int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+        if (ex.chunk > 0 && pos >= 0) lo = max(lo, (pos / ex.chunk) * ex.chunk);
+        return lo;
+    };
+    const int lo0 = first_seen(pos0), lo1 = first_seen(pos1);
+    const float* bias0 = ex.bias != nullptr ? ex.bias + (size_t)(kvh * group + r0 % group) * ex.bias_len : nullptr;
+    const float* bias1 = ex.bias != nullptr ? ex.bias + (size_t)(kvh * group + r1 % group) * ex.bias_len : nullptr;
 
     unsigned qf[KS][4];
     {
@@ -103,7 +110,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
 
     // Keys [key_lo, key_hi) are visible to some row of the block.
     const int pos_first = start + j0, pos_last = start + j0 + n_tok - 1;
-    const int key_lo = (window > 0 && pos_first + 1 > window) ? pos_first + 1 - window : 0;
+    const int key_lo = first_seen(pos_first), key_lo_last = first_seen(pos_last);
     const int t_lo = key_lo / PF_PAGE, t_hi = pos_last / PF_PAGE + 1;
 
     auto issue = [&](int tile, int stage) {
@@ -146,7 +153,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
         }
         const int key_base = tile * PF_PAGE;
         // Element-wise masking only where some row of the block has its border inside the tile.
-        const bool need_mask = key_base + PF_PAGE - 1 > pos_first || key_base < key_lo + (window > 0 ? n_tok : 0) ||
+        const bool need_mask = key_base + PF_PAGE - 1 > pos_first || key_base < key_lo + (window > 0 ? n_tok : 0) || key_base < key_lo_last ||
                                n_tok * group < PF_ROWS;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -155,6 +162,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
             for (int j = 0; j < 2; ++j) {
                 const int key = key_base + 8 * nt + 2 * t + j;
                 float a = s[nt][j] * scale_log2e, c = s[nt][2 + j] * scale_log2e;
+                if (bias0 != nullptr) {                      // the bias of the distance, per row's head; rows that do not see the key are masked below
+                    a += bias0[min(max(pos0 - key, 0), ex.bias_len - 1)];
+                    c += bias1[min(max(pos1 - key, 0), ex.bias_len - 1)];
+                }
                 if (need_mask) {
                     if (key > pos0 || key < lo0) a = -INFINITY;
                     if (key > pos1 || key < lo1) c = -INFINITY;
@@ -221,7 +232,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
 template <int D>
 static int launch_prefill(bf16* out, const bf16* q, const bf16* k, const bf16* v, const int* table, int table_stride,
                           const int* seq_slots, const int* cu_seqlens, const int* kv_lens, int n_seqs, int total_tiles,
-                          float scale, int nq, int nkv, int tokens_per_tile, int window, const float* sink, cudaStream_t stream) {
+                          float scale, int nq, int nkv, int tokens_per_tile, int window, const float* sink, AttnExtras ex, cudaStream_t stream) {
     static bool configured = false;
     const size_t smem = PrefillSmem<D>::BYTES;
     if (!configured) {
@@ -232,7 +243,7 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* k, const bf16* v
     dim3 grid(total_tiles, nkv);
     ti_launch(attention_prefill_kernel<D>, dim3(grid), dim3(PF_THREADS), smem, stream, out, q, k, v, table, table_stride, seq_slots, cu_seqlens,
                                                                    kv_lens, n_seqs, scale * 1.4426950408889634f, nq, nkv,
-                                                                   tokens_per_tile, window, sink);
+                                                                   tokens_per_tile, window, sink, ex);
     return ti_check_launch("attention_prefill");
 }
 
@@ -240,11 +251,15 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* k, const bf16* v
 // tokens_per_tile = 128 / (query heads per KV head). Returns 2 when the sizes are outside what the
 // kernel takes (the caller then runs the plain kernel).
 // `sink` [nq] float (or null): one more term exp(sink[head]) in every softmax's denominator.
-extern "C" int ti_attention_prefill_sink(void* out, const void* q, const void* k_cache, const void* v_cache,
+// `chunk`, `dist_bias` [nq][bias_len] (times log2 e), `bias_len`: see AttnExtras.
+extern "C" int ti_attention_prefill_biased(void* out, const void* q, const void* k_cache, const void* v_cache,
                                          const int* block_table, int table_stride, const int* seq_slots,
                                          const int* cu_seqlens, const int* kv_lens, int n_seqs, int total_tiles, float scale,
-                                         int nq, int nkv, int D, int page_size, int window, const float* sink, cudaStream_t stream) {
+                                         int nq, int nkv, int D, int page_size, int window, const float* sink, int chunk, const float* dist_bias, int bias_len,
+                                           cudaStream_t stream) {
+    const AttnExtras ex = {chunk, dist_bias, bias_len};
     if (n_seqs == 0 || total_tiles == 0) return 0;
+    TI_REQUIRE(chunk >= 0 && (dist_bias == nullptr || bias_len > 0), "attention_prefill: chunk %d, bias table of %d", chunk, bias_len);
     if (page_size != PF_PAGE || nq % nkv != 0 || nq / nkv > PF_ROWS || D % 16 != 0 || nkv > 65535) {
         ti_fail("attention_prefill takes page size %d, at most %d query heads per KV head and head sizes in steps of 16; "
                 "got page %d, %d/%d heads, head size %d", PF_PAGE, PF_ROWS, page_size, nq, nkv, D);
@@ -255,7 +270,7 @@ extern "C" int ti_attention_prefill_sink(void* out, const void* q, const void* k
     case d:                                                                                                            \
         return launch_prefill<d>((bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,    \
                                  table_stride, seq_slots, cu_seqlens, kv_lens, n_seqs, total_tiles, scale, nq, nkv,    \
-                                 tokens_per_tile, window, sink, stream);
+                                 tokens_per_tile, window, sink, ex, stream);
     switch (D) {
         PF_CASE(16) PF_CASE(32) PF_CASE(48) PF_CASE(64) PF_CASE(80) PF_CASE(96) PF_CASE(112) PF_CASE(128) PF_CASE(256)
         default:
@@ -263,6 +278,14 @@ extern "C" int ti_attention_prefill_sink(void* out, const void* q, const void* k
             return 2;
     }
 #undef PF_CASE
+}
+
+extern "C" int ti_attention_prefill_sink(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                         const int* block_table, int table_stride, const int* seq_slots,
+                                         const int* cu_seqlens, const int* kv_lens, int n_seqs, int total_tiles, float scale,
+                                         int nq, int nkv, int D, int page_size, int window, const float* sink, cudaStream_t stream) {
+    return ti_attention_prefill_biased(out, q, k_cache, v_cache, block_table, table_stride, seq_slots, cu_seqlens, kv_lens, n_seqs, total_tiles,
+                                       scale, nq, nkv, D, page_size, window, sink, 0, nullptr, 0, stream);
 }
 
 extern "C" int ti_attention_prefill(void* out, const void* q, const void* k_cache, const void* v_cache,

@@ -213,6 +213,16 @@ template <> struct Vec16<bf16> {
 };
 __host__ __forceinline__ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
+// Two more rules of visibility and score for the paged attention kernels. chunk > 0: a key is visible only inside the query's
+// chunk of so many positions, floor(i / chunk) = floor(j / chunk), counted from the sequence's start. bias [heads][bias_len]
+// (null: none): entry [head][min(i - j, bias_len - 1)] is added to the scaled score; the kernels that work in base 2 get the
+// table already times log2(e).
+struct AttnExtras {
+    int chunk;
+    const float* bias;
+    int bias_len;
+};
+
 #define TI_DISPATCH_DTYPE(dtype, ...)                                   \
     do {                                                                \
         if ((dtype) == TI_F32) { typedef float T; __VA_ARGS__; }        \

@@ -12,7 +12,8 @@
 template <int D>
 __device__ __forceinline__ void decode_tile(const bf16* kt, const bf16* vt, const unsigned (&qf)[D / 16][4], float (&o)[D / 8][4],
                                             float& m0, float& m1, float& l0, float& l1, int tile, int warp, int lane,
-                                            int kv_len, int first_key, float scale_log2e) {
+                                            int kv_len, int first_key, float scale_log2e, const float* __restrict__ bias0 = nullptr,
+                                            const float* __restrict__ bias1 = nullptr, int bias_len = 0) {
     constexpr int CPR = D / 8, KS = D / 16, NT = D / 8;
     const int t = lane & 3;
         float s[2][4];
@@ -39,8 +40,13 @@ __device__ __forceinline__ void decode_tile(const bf16* kt, const bf16* vt, cons
         for (int j = 0; j < 2; ++j) {
             const int key = key0 + 8 * nt + j;
             const bool ok = key < kv_len && key >= first_key;
-            s[nt][j] = ok ? s[nt][j] * scale_log2e : -INFINITY;
-            s[nt][2 + j] = ok ? s[nt][2 + j] * scale_log2e : -INFINITY;
+            float add0 = 0.f, add1 = 0.f;
+            if (bias0 != nullptr && ok) {                    // the bias of the distance from the step's token, per row's head
+                const int dist = min(kv_len - 1 - key, bias_len - 1);
+                add0 = bias0[dist]; add1 = bias1[dist];
+            }
+            s[nt][j] = ok ? fmaf(s[nt][j], scale_log2e, add0) : -INFINITY;
+            s[nt][2 + j] = ok ? fmaf(s[nt][2 + j], scale_log2e, add1) : -INFINITY;
             mx0 = fmaxf(mx0, s[nt][j]);
             mx1 = fmaxf(mx1, s[nt][2 + j]);
         }

@@ -26,8 +26,8 @@ Further options. ``norm_weight`` False: the norms of q and k have no weight (eve
 inside the query's chunk of c positions, floor(i / c) = floor(j / c), counted from the sequence's start. ``distance_bias`` far: a
 learned table ``rel`` [rows, heads] adds rel[bucket(i - j), head] to the scaled score, bucket(n) = n for n < rows / 2 and
 min(rows - 1, rows / 2 + floor(ln(n / (rows / 2)) / ln(far / (rows / 2)) * (rows - rows / 2))) beyond: one row per small distance,
-logarithmic steps up to ``far``, the last row from there on. Attention with a chunk or a distance bias runs in the plain paged kernel
-in every element type.
+logarithmic steps up to ``far``, the last row from there on. In bfloat16 attention with a chunk or a distance bias runs in the
+``mma.sync`` prompt kernel and the split-KV decode kernel (the bias comes as a table by distance), in 32-bit in the plain kernel.
 
 Record: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``, ``window``, ``kv_source``, ``qk_norm_eps`` and the options
 ``value_dim``, ``conv_taps`` (0: none), ``bias``, ``out_bias``, ``row_norm``, ``head_norm``, ``norm_weight``, ``sink``, ``gate``,
@@ -97,7 +97,7 @@ class ConvAttention(Mixer):
             self.q_norm = get(n["q"] + n["norm_suffix"]) if self.row_norm else None
             self.k_norm = get(n["k"] + n["norm_suffix"]) if self.row_norm and self.own_kv else None
         self.chunk = int(o.get("chunk") or 0)
-        self.distance_bias = None
+        self.distance_bias = self.distance_bias2 = None
         if o.get("distance_bias"):
             rel = rt.param(tensors[p + n["rel"]], keep_dtype=True).float()           # [rows, heads]
             far = float(o["distance_bias"])
@@ -107,6 +107,7 @@ class ConvAttention(Mixer):
             count = int(math.ceil(far)) + 1                                            # from `far` on every distance has the last row
             index = torch.tensor(distance_buckets(rel.shape[0], far, count), dtype=torch.long, device=rel.device)
             self.distance_bias = rel[index].t().contiguous()                          # [heads, count]: the bias by distance
+            self.distance_bias2 = (self.distance_bias * 1.4426950408889634).contiguous()      # for the kernels that work in base 2
         self.out_name, self.gated_name = "mixer.delta", "conv_attention.gated"
         self.sink = rt.param(tensors[p + n["sink"]], keep_dtype=True).float().contiguous() if self.sink_on else None
         self.o = Linear(get(n["o"]), rt, "o")
@@ -153,7 +154,7 @@ class ConvAttention(Mixer):
         return tuple(out)
 
     def decode_plan(self, group):
-        if not (self.rt.fast and self.rt.dtype == torch.bfloat16) or not self.own_kv or self.chunk or self.distance_bias is not None:
+        if not (self.rt.fast and self.rt.dtype == torch.bfloat16) or not self.own_kv:
             return None
         from ..kernels import fast
         return fast.SplitKvPlan(self.nkv, group.page_size, group.num_pages * group.page_size)
@@ -173,9 +174,9 @@ class ConvAttention(Mixer):
             ops.conv_state_update(cache.state, rows, self.bias, self.taps, step, C)
         attn = rt.buffer("attention.out", (n, nq * Dp))
         done = False
-        if rt.fast and not self.chunk and self.distance_bias is None:
+        if rt.fast:
             from ..kernels import fast
-            done = fast.attention(attn, q, cache, meta, step, self.attn_spec, sink=self.sink)
+            done = fast.attention(attn, q, cache, meta, step, self.attn_spec, sink=self.sink, chunk=self.chunk, distance_bias2=self.distance_bias2)
         if not done:
             ops.attention_plain(attn, q, cache.k, cache.v, meta.block_table, step.tok_slot, step.positions, s.scale, nq, nkv, Dp,
                                 cache.page_size, window=s.window or 0, sink=self.sink, chunk=self.chunk, distance_bias=self.distance_bias)
