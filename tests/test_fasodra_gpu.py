@@ -573,6 +573,106 @@ def test_stream_copies_and_small_kernels_alone():
         assert float((out_t.float().cpu() - torch.relu(z) ** 2).abs().max()) <= (1e-6 if T == torch.float32 else 2.0 ** -8) * 10
 
 
+def _dense_attention(q, k, v, scale, start, chunk, bias):
+    """q [n, H, D] at positions start .. start + n - 1 over keys k, v [L, G, D]: exact attention in 64-bit with the chunk rule and
+    the bias table [H, count] by distance."""
+    n, H, D = q.shape
+    L, G, _ = k.shape
+    qp, kp = torch.arange(start, start + n)[:, None], torch.arange(L)[None, :]
+    vis = kp <= qp
+    if chunk:
+        vis &= (kp // chunk) == (qp // chunk)
+    out = torch.zeros(n, H, D, dtype=F64)
+    for h in range(H):
+        s = (q[:, h].double() @ k[:, h // (H // G)].double().T) * scale
+        if bias is not None:
+            s = s + bias[h].double()[(qp - kp).clamp(0, bias.shape[1] - 1)]
+        out[:, h] = torch.softmax(s.masked_fill(~vis, float("-inf")), -1) @ v[:, h // (H // G)].double()
+    return out
+
+
+@pytest.mark.parametrize("nq,nkv,D,chunk,count", [(8, 2, 64, 100, 241), (6, 3, 32, 64, 0), (16, 1, 128, 7, 30), (40, 2, 64, 0, 500), (4, 4, 96, 333, 64)])
+def test_chunked_and_biased_attention_kernels_alone(nq, nkv, D, chunk, count):
+    """The three paged kernels that take the chunk rule and the bias by distance (plain, the prompt kernel on ``mma.sync``, the
+    split-KV decode kernel with 1 to 32 parts) against exact attention: sequences of unequal lengths, some continuing from cached
+    positions, shuffled pages, chunks that are no multiple of a page, more than sixteen query heads per key/value head, distances
+    beyond the table's end. One key that lies just outside the last query's chunk is made huge and must not show."""
+    from test_kernels_gpu import close, dev, paged
+    from tileinfer_b200.kernels import ops
+    from tileinfer_b200.kernels.library import check, lib
+    torch.manual_seed(17)
+    dtype = torch.bfloat16
+    r = lambda x: x.to(dtype).float()
+    total = [300, 1, 130, 513, 64]                  # cached length after the step
+    fresh = [300, 1, 30, 200, 64]                   # tokens of the step (the rest was cached before)
+    B = len(total)
+    ks = [r(torch.randn(L, nkv, D)) for L in total]
+    vs = [r(torch.randn(L, nkv, D)) for L in total]
+    qs = [r(torch.randn(n, nq, D)) for n in fresh]
+    if chunk:
+        edge = (512 // chunk) * chunk                # the first key of the last query's chunk in sequence 3
+        if edge > 0:
+            ks[3][edge - 1] = r(qs[3][-1, 1] * 9.0)[None].expand(nkv, D)
+    bias = torch.randn(nq, count) * 1.5 if count else None
+    scale = 1 / math.sqrt(D)
+    n_pages = sum(-(-L // 64) for L in total) + 3
+    kp, vp, table = paged(ks, vs, 64, n_pages, 13, dtype)
+    want = torch.cat([_dense_attention(qs[b], ks[b], vs[b], scale, total[b] - fresh[b], chunk, bias) for b in range(B)]).float()
+    q = dev(torch.cat(qs), dtype)
+    cu = [0]
+    for n in fresh:
+        cu.append(cu[-1] + n)
+    bias_d = dev(bias) if bias is not None else None
+    bias2 = dev(bias * 1.4426950408889634) if bias is not None else None
+    slots, cu_d, lens_d = (dev(torch.arange(1, B + 1, dtype=torch.int32)), dev(torch.tensor(cu, dtype=torch.int32)),
+                           dev(torch.tensor(total, dtype=torch.int32)))
+    tok_slot = dev(torch.cat([torch.full((n,), b + 1, dtype=torch.int32) for b, n in enumerate(fresh)]))
+    positions = dev(torch.cat([torch.arange(total[b] - fresh[b], total[b], dtype=torch.int32) for b in range(B)]))
+    out = torch.full((cu[-1], nq, D), float("nan"), dtype=dtype, device="cuda")
+    ops.attention_plain(out, q, kp, vp, table, tok_slot, positions, scale, nq, nkv, D, 64, chunk=chunk, distance_bias=bias_d)
+    close(out, want, dtype, ulps=5.0)
+    st = torch.cuda.current_stream().cuda_stream
+    tpt = 128 // (nq // nkv)
+    tiles = sum(-(-n // tpt) for n in fresh)
+    out = torch.full((cu[-1], nq, D), float("nan"), dtype=dtype, device="cuda")
+    check(lib().ti_attention_prefill_biased(out.data_ptr(), q.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(), table.stride(0),
+                                            slots.data_ptr(), cu_d.data_ptr(), lens_d.data_ptr(), B, tiles, scale, nq, nkv, D, 64, 0, None, chunk,
+                                            bias2.data_ptr() if bias2 is not None else None, count, st), "attention_prefill")
+    close(out, want, dtype, ulps=5.0)
+    # one token per sequence: the last query of each
+    last = [c - 1 for c in cu[1:]]
+    qd = dev(torch.cat(qs)[last], dtype)
+    for splits in (1, 3, 32):
+        out = torch.full((B, nq, D), float("nan"), dtype=dtype, device="cuda")
+        ws_o = torch.full((B * splits, nq, D), float("nan"), device="cuda")
+        ws_ml = torch.full((B * splits, nq, 2), float("nan"), device="cuda")
+        check(lib().ti_attention_decode_biased(out.data_ptr(), qd.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(), table.stride(0),
+                                               slots.data_ptr(), lens_d.data_ptr(), None, None, ws_o.data_ptr(), ws_ml.data_ptr(), scale, B, nq, nkv,
+                                               D, 64, splits, 0, None, chunk, bias2.data_ptr() if bias2 is not None else None, count, st), "attention_decode")
+        close(out, want[last], dtype, ulps=5.0)
+
+
+def test_bfloat16_steps_take_the_fast_kernels(models):
+    """Case B's sizes are ones the fast kernels take: a prompt and a one-token step in bfloat16 go through the tensor-core products,
+    the grouped products of the experts and the paged attention kernels (those with the chunk rule and the bias in the biased
+    layers), not through their plain stand-ins."""
+    from tileinfer_b200.kernels import library
+    m = models["B"]
+    engine = m.engine("bfloat16", graphs=False)
+    slot = engine.new_sequence()
+    library.call_counts.clear()
+    engine.step([(slot, fc.prompts(m.vocab, [600], 61)[0])])
+    engine.step([(slot, [5])])
+    engine.free_sequence(slot)
+    engine.check_health()
+    used = dict(library.call_counts)
+    assert used.get("ti_attention_prefill_biased", 0) == 2 and used.get("ti_attention_decode_biased", 0) == 2, used
+    assert used.get("ti_attention_prefill_tc", 0) + used.get("ti_attention_prefill", 0) == 2 and used.get("ti_attention_decode_shared", 0) == 2, used
+    assert used.get("ti_decay_scan", 0) == 2 and used.get("ti_delta_scan", 0) == 2 and used.get("ti_streams_update", 0) == 16, used
+    assert used.get("ti_gemm_tcgen05", 0) > 0 and used.get("ti_gemm_tcgen05_grouped", 0) > 0, used
+    assert "ti_attention_plain" not in used and "ti_attention_plain_biased" not in used, used
+
+
 # ---------------------------------------------------------------- through the public entry points
 def test_greedy_generation_through_the_public_entry_point(models):
     """``generate`` (batches, scheduler, sampler, decode loop) on several prompts at once, more than there are slots, in 32-bit:
