@@ -742,7 +742,7 @@ def main(argv=None) -> int:
     if args.preset == "vogilix":
         return run_vogilix(args, *peaks())
     if args.preset == "fasodra":
-        return run_fasodra(args, pk, pk_source)
+        return run_fasodra(args, *peaks())
     if args.preset == "sozanex":
         return run_sozanex(args, *peaks())
     if args.preset == "zudepel":

@@ -362,7 +362,7 @@ def test_decay_scan_alone():
     from tileinfer_b200.kernels import ops
     g = torch.Generator().manual_seed(11)
     for T in (torch.float32, torch.bfloat16):
-        for H, D in ((3, 24), (2, 64), (1, 130)):
+        for H, D in ((3, 24), (2, 64), (1, 130), (20, 64), (5, 64)):          # the last two: blocks of 32 and of 16 columns
             HD, extra = H * D, 5
             lengths = [70, 1, 23]
             total = sum(lengths)
@@ -414,7 +414,7 @@ def test_delta_scan_alone():
     query/key heads, unequal sequences, portions continued from the state."""
     from tileinfer_b200.kernels import ops
     g = torch.Generator().manual_seed(12)
-    for H, G, D, V in ((4, 2, 24, 40), (2, 2, 64, 32), (1, 1, 130, 70), (6, 1, 16, 16)):
+    for H, G, D, V in ((4, 2, 24, 40), (2, 2, 64, 32), (1, 1, 130, 70), (6, 1, 16, 16), (20, 4, 32, 64), (5, 5, 48, 64)):      # the last two: blocks of 32 and of 16 columns
         C = 2 * G * D + H * V
         lengths = [50, 1, 19]
         total = sum(lengths)
