@@ -64,24 +64,27 @@ __global__ void decay_scan_kernel(float* __restrict__ o, const T* rkv, long long
         s[r] = in ? __ldcg(S + (size_t)(row0 + r) * D + col) : 0.f;
         bonus[r] = row0 + r < D ? u[h * D + row0 + r] : 0.f;
     }
-    float fr[PER], fk[PER], fd[PER], fv[PV];
+    // Fetched values stay as they were loaded (no conversion, no branch): a use right behind a load would make the warp wait for it,
+    // one round trip to memory per load instead of one per batch. Rows outside the batch or the head read a valid address and
+    // are zeroed when they are laid into shared memory.
+    T fr[PER], fk[PER], fv[PV];
+    float fd[PER];
     auto fetch = [&](int base, int count) {
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const int e = threadIdx.x + j * threads, i = e / Dp, d = e - i * Dp;
-            fr[j] = 0.f; fk[j] = 0.f; fd[j] = 0.f;
-            if (i < count && d < D) {
-                const T* row = rkv + (size_t)(base + i) * ld + h * D + d;
-                fr[j] = to_f32(__ldcg(row + r_off));
-                fk[j] = to_f32(__ldcg(row + k_off));
-                fd[j] = __ldcg(dlog + (size_t)(base + i) * H * D + h * D + d);
-            }
+            const bool in = i < count && d < D;
+            const size_t at = in ? (size_t)(base + i) * ld + h * D + d : 0;
+            fr[j] = __ldcg(rkv + at + r_off);
+            fk[j] = __ldcg(rkv + at + k_off);
+            fd[j] = __ldcg(dlog + (in ? (size_t)(base + i) * H * D + h * D + d : 0));
         }
         if (early_v) {
 #pragma unroll
             for (int j = 0; j < PV; ++j) {
                 const int e = threadIdx.x + j * threads, i = e / CB, c = col0 + e % CB;
-                fv[j] = (e < RS_BATCH * CB && i < count && c < D) ? to_f32(__ldcg(rkv + (size_t)(base + i) * ld + v_off + h * D + c)) : 0.f;
+                const bool in = e < RS_BATCH * CB && i < count && c < D;
+                fv[j] = __ldcg(rkv + (in ? (size_t)(base + i) * ld + v_off + h * D + c : 0));
             }
         }
     };
@@ -90,15 +93,15 @@ __global__ void decay_scan_kernel(float* __restrict__ o, const T* rkv, long long
         for (int j = 0; j < PER; ++j) {
             const int e = threadIdx.x + j * threads, i = e / Dp, d = e - i * Dp;
             const bool in = i < count && d < D;
-            sr[buf * RS_BATCH * Dp + e] = fr[j];
-            sk[buf * RS_BATCH * Dp + e] = fk[j];
+            sr[buf * RS_BATCH * Dp + e] = in ? to_f32(fr[j]) : 0.f;
+            sk[buf * RS_BATCH * Dp + e] = in ? to_f32(fk[j]) : 0.f;
             sw[buf * RS_BATCH * Dp + e] = in ? expf(-expf(fd[j] + w0[h * D + d])) : 1.f;
         }
         if (early_v) {
 #pragma unroll
             for (int j = 0; j < PV; ++j) {
-                const int e = threadIdx.x + j * threads;
-                if (e < RS_BATCH * CB) sv[buf * RS_BATCH * CB + e] = fv[j];
+                const int e = threadIdx.x + j * threads, i = e / CB, c = col0 + e % CB;
+                if (e < RS_BATCH * CB) sv[buf * RS_BATCH * CB + e] = (i < count && c < D) ? to_f32(fv[j]) : 0.f;
             }
         } else {                                  // a block of few threads (a small key size) reads its values late
             for (int e = threadIdx.x; e < RS_BATCH * CB; e += threads) {
@@ -226,7 +229,7 @@ extern "C" int ti_decay_scan(float* o, const void* rkv, long long ld, int r_off,
     // Very few (sequence, head) pairs: blocks of 16 or 8 columns, so that more SMs have one (the state's rows of a column are then
     // shared out among the lanes of a warp as well as among the warps). Every block stages all key rows of its head, so narrower
     // blocks multiply that work: with 64 blocks of 32 columns already (32 heads of 64, one prompt of 2,048 tokens) blocks of 16
-    // columns were slower (1,197 against 797 us), hence only below a quarter of the SMs.
+    // columns were slower (551 against 465 us), hence only below a quarter of the SMs.
     const long long blocks32 = (long long)((D + 31) / 32) * H * B;
     const int sms = ti_sm_count();
 #define RS_DECAY(R, CB) launch_decay_scan<T, R, CB>(o, (const T*)rkv, ld, r_off, k_off, v_off, dlog, w0, u, state, state_stride, cu_seqlens, seq_slots, B, H, D, n == B, stream)
