@@ -591,10 +591,11 @@ def _dense_attention(q, k, v, scale, start, chunk, bias):
     return out
 
 
-@pytest.mark.parametrize("nq,nkv,D,chunk,count", [(8, 2, 64, 100, 241), (6, 3, 32, 64, 0), (16, 1, 128, 7, 30), (40, 2, 64, 0, 500), (4, 4, 96, 333, 64)])
+@pytest.mark.parametrize("nq,nkv,D,chunk,count", [(8, 2, 64, 100, 241), (6, 3, 32, 64, 0), (16, 1, 128, 7, 30), (40, 2, 64, 0, 500), (4, 4, 96, 333, 64),
+                                                  (16, 4, 128, 256, 0), (4, 4, 64, 0, 0)])
 def test_chunked_and_biased_attention_kernels_alone(nq, nkv, D, chunk, count):
-    """The three paged kernels that take the chunk rule and the bias by distance (plain, the prompt kernel on ``mma.sync``, the
-    split-KV decode kernel with 1 to 32 parts) against exact attention: sequences of unequal lengths, some continuing from cached
+    """The paged kernels that take the chunk rule and the bias by distance (plain, the prompt kernels on ``mma.sync`` and, for heads of
+    64 and 128, on tensor memory, the split-KV decode kernel with 1 to 32 parts) against exact attention: sequences of unequal lengths, some continuing from cached
     positions, shuffled pages, chunks that are no multiple of a page, more than sixteen query heads per key/value head, distances
     beyond the table's end. One key that lies just outside the last query's chunk is made huge and must not show."""
     from test_kernels_gpu import close, dev, paged
@@ -639,6 +640,18 @@ def test_chunked_and_biased_attention_kernels_alone(nq, nkv, D, chunk, count):
                                             slots.data_ptr(), cu_d.data_ptr(), lens_d.data_ptr(), B, tiles, scale, nq, nkv, D, 64, 0, None, chunk,
                                             bias2.data_ptr() if bias2 is not None else None, count, st), "attention_prefill")
     close(out, want, dtype, ulps=5.0)
+    if D in (64, 128):
+        from tileinfer_b200.kernels import fast
+        tpb = 2 * (128 // (nq // nkv))
+        blocks = sum(-(-n // tpb) for n in fresh)
+        status = fast.status_word()
+        out = torch.full((cu[-1], nq, D), float("nan"), dtype=dtype, device="cuda")
+        check(lib().ti_attention_prefill_tc_biased(out.data_ptr(), q.data_ptr(), kp.data_ptr(), vp.data_ptr(), kp.shape[0], table.data_ptr(), table.stride(0),
+                                                   slots.data_ptr(), cu_d.data_ptr(), lens_d.data_ptr(), B, cu[-1], blocks, scale, nq, nkv, D, 64, 0,
+                                                   status.data_ptr(), None, chunk, bias2.data_ptr() if bias2 is not None else None, count, st),
+              "attention_prefill_tc")
+        fast.check_status()
+        close(out, want, dtype, ulps=5.0)
     # one token per sequence: the last query of each
     last = [c - 1 for c in cu[1:]]
     qd = dev(torch.cat(qs)[last], dtype)
@@ -666,11 +679,11 @@ def test_bfloat16_steps_take_the_fast_kernels(models):
     engine.free_sequence(slot)
     engine.check_health()
     used = dict(library.call_counts)
-    assert used.get("ti_attention_prefill_biased", 0) == 2 and used.get("ti_attention_decode_biased", 0) == 2, used
+    assert used.get("ti_attention_prefill_tc_biased", 0) == 2 and used.get("ti_attention_decode_biased", 0) == 2, used
     assert used.get("ti_attention_prefill_tc", 0) + used.get("ti_attention_prefill", 0) == 2 and used.get("ti_attention_decode_shared", 0) == 2, used
     assert used.get("ti_decay_scan", 0) == 2 and used.get("ti_delta_scan", 0) == 2 and used.get("ti_streams_update", 0) == 16, used
     assert used.get("ti_gemm_tcgen05", 0) > 0 and used.get("ti_gemm_tcgen05_grouped", 0) > 0, used
-    assert "ti_attention_plain" not in used and "ti_attention_plain_biased" not in used, used
+    assert "ti_attention_plain" not in used and "ti_attention_plain_biased" not in used and "ti_attention_prefill_biased" not in used, used
 
 
 # ---------------------------------------------------------------- through the public entry points

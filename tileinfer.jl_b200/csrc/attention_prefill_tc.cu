@@ -41,6 +41,7 @@ struct Params {
     float scale_log2;
     int* status;
     const float* sink;         // [heads] or null: exp(sink[head]) more in every softmax's denominator
+    AttnExtras ex;             // chunked visibility and a bias by distance (times log2 e), see common.cuh
 };
 
 template <int D> struct Cfg {
@@ -118,7 +119,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     const int t_end = min(q_len, t0 + tokens_per_block);
     // Keys [key_lo, key_hi) can matter to some row of the block.
     const int key_hi = start + t_end;
-    const int key_lo = p.window > 0 ? max(0, start + t0 - p.window + 1) : 0;
+    int key_lo = p.window > 0 ? max(0, start + t0 - p.window + 1) : 0;
+    if (p.ex.chunk > 0) key_lo = max(key_lo, ((start + t0) / p.ex.chunk) * p.ex.chunk);        // the chunk of the block's first token
     const int j_lo = key_lo / KEYS, j_hi = (key_hi + KEYS - 1) / KEYS;
     const int n_pages = (kv_len + PAGE - 1) / PAGE;
 
@@ -245,6 +247,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         const unsigned lane_base = tmem_base + ((unsigned)((warp & 3) * 32) << 16);
         const unsigned s_addr = lane_base + x * KEYS, o_addr = lane_base + C::O_COL + x * D;
         float m_used = -1e30f, l = 0.f;
+        const float score_scale = p.ex.bias != nullptr ? 1.0f : p.scale_log2;      // with a bias the scores are scaled where it is added
         bool ok = true;
         for (int j = j_lo; ok && j < j_hi; ++j) {
             const unsigned jphase = (unsigned)(j - j_lo) & 1u;
@@ -253,13 +256,28 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
             tc_fence_after();
             const int key0 = j * KEYS;
             // Warp-uniform: does any row of this warp have a masked key in this step?
-            const bool masked = key0 + KEYS - 1 > warp_pos_lo || (p.window > 0 && key0 <= warp_pos_hi - p.window);
-            const int k_hi = pos, k_lo = p.window > 0 ? pos - p.window + 1 : 0;        // the row sees keys [k_lo, k_hi]
+            const bool masked = key0 + KEYS - 1 > warp_pos_lo || (p.window > 0 && key0 <= warp_pos_hi - p.window) ||
+                                (p.ex.chunk > 0 && key0 < (warp_pos_hi / p.ex.chunk) * p.ex.chunk);
+            int k_lo = p.window > 0 ? pos - p.window + 1 : 0;                          // the row sees keys [k_lo, k_hi]
+            if (p.ex.chunk > 0) k_lo = max(k_lo, (pos / p.ex.chunk) * p.ex.chunk);
+            const int k_hi = pos;
             // The whole row of scores in registers: four loads in flight, one wait.
             unsigned r[4][32];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, r[c]);
             tmem_ld_wait();
+            if (p.ex.bias != nullptr) {
+                // A bias by the distance to the key, added to the scaled score: from here on the scores are in base-2 units
+                // (the scale below is then one). Keys that the row does not see are masked afterwards.
+                const float* __restrict__ brow = p.ex.bias + (size_t)head * p.ex.bias_len;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int dist = min(max(pos - (key0 + c * 32 + i), 0), p.ex.bias_len - 1);
+                        r[c][i] = __float_as_uint(fmaf(__uint_as_float(r[c][i]), p.scale_log2, __ldg(brow + dist)));
+                    }
+            }
             if (masked) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
@@ -275,7 +293,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
 #pragma unroll
                 for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[c][i]));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float mt = fmaxf(mx * p.scale_log2, -1e30f);
+            const float mt = fmaxf(mx * score_scale, -1e30f);
             if (j == j_lo) {
                 m_used = mt;
             } else if (__any_sync(0xffffffffu, mt > m_used + RESCALE_STEP)) {
@@ -299,7 +317,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
                 tmem_st_wait();
             }
             f32x2 l2[2] = {0ull, 0ull};                          // two chains of packed sums
-            const f32x2 scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(-m_used, -m_used);
+            const f32x2 scale2 = pack2(score_scale, score_scale), neg_m2 = pack2(-m_used, -m_used);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 unsigned packed[16];
@@ -386,12 +404,14 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 // non-zero value afterwards means a wait ran out. Returns 2 when the sizes are outside what this kernel
 // takes (head size 64 or 128, 1 to 128 query heads per KV head, pages of 64): the caller then runs the
 // kernel for all sizes.
-extern "C" int ti_attention_prefill_tc_sink(void* out, const void* q, const void* k_cache, const void* v_cache, int n_pages,
-                                            const int* block_table, int table_stride, const int* seq_slots,
-                                            const int* cu_seqlens, const int* kv_lens, int n_seqs, int n_tokens, int total_blocks,
-                                            float scale, int nq, int nkv, int D, int page_size, int window, int* status,
-                                            const float* sink, cudaStream_t stream) {
+// `chunk`, `dist_bias` [nq][bias_len] (times log2 e), `bias_len`: see AttnExtras.
+extern "C" int ti_attention_prefill_tc_biased(void* out, const void* q, const void* k_cache, const void* v_cache, int n_pages,
+                                              const int* block_table, int table_stride, const int* seq_slots,
+                                              const int* cu_seqlens, const int* kv_lens, int n_seqs, int n_tokens, int total_blocks,
+                                              float scale, int nq, int nkv, int D, int page_size, int window, int* status,
+                                              const float* sink, int chunk, const float* dist_bias, int bias_len, cudaStream_t stream) {
     if (n_seqs == 0 || total_blocks == 0) return 0;
+    TI_REQUIRE(chunk >= 0 && (dist_bias == nullptr || bias_len > 0), "attention_prefill_tc: chunk %d, bias table of %d", chunk, bias_len);
     const int group = nkv > 0 ? nq / nkv : 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || group < 1 || group > ROWS || (D != 64 && D != 128) || nkv > 65535 ||
         ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15)) {
@@ -404,6 +424,7 @@ extern "C" int ti_attention_prefill_tc_sink(void* out, const void* q, const void
     p.out = (bf16*)out; p.table = block_table; p.table_stride = table_stride; p.slots = seq_slots; p.cu_seqlens = cu_seqlens;
     p.kv_lens = kv_lens; p.n_seqs = n_seqs; p.heads = nq; p.kv_heads = nkv; p.group = group; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.sink = sink;
+    p.ex = AttnExtras{chunk, dist_bias, bias_len};
     CUtensorMap mq, mk, mv;
     {
         const unsigned long long dims[3] = {(unsigned long long)D, (unsigned long long)nq, (unsigned long long)n_tokens};
@@ -420,6 +441,15 @@ extern "C" int ti_attention_prefill_tc_sink(void* out, const void* q, const void
     }
     return D == 64 ? launch<64>(mq, mk, mv, (const bf16*)q, p, total_blocks, stream)
                    : launch<128>(mq, mk, mv, (const bf16*)q, p, total_blocks, stream);
+}
+
+extern "C" int ti_attention_prefill_tc_sink(void* out, const void* q, const void* k_cache, const void* v_cache, int n_pages,
+                                            const int* block_table, int table_stride, const int* seq_slots,
+                                            const int* cu_seqlens, const int* kv_lens, int n_seqs, int n_tokens, int total_blocks,
+                                            float scale, int nq, int nkv, int D, int page_size, int window, int* status,
+                                            const float* sink, cudaStream_t stream) {
+    return ti_attention_prefill_tc_biased(out, q, k_cache, v_cache, n_pages, block_table, table_stride, seq_slots, cu_seqlens, kv_lens, n_seqs,
+                                          n_tokens, total_blocks, scale, nq, nkv, D, page_size, window, status, sink, 0, nullptr, 0, stream);
 }
 
 extern "C" int ti_attention_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache, int n_pages,

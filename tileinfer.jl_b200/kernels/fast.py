@@ -298,8 +298,7 @@ SHORT_STEP = 512
 def attention(out, q, cache, meta, step, spec, sink=None, chunk=0, distance_bias2=None) -> bool:
     """``sink`` [heads] float32: one more term exp(sink[head]) in every softmax's denominator. ``chunk`` > 0: a key is visible only
     inside the query's chunk of so many positions; ``distance_bias2`` [heads, L] float32: the bias by distance times log2(e) (the
-    kernels work in base 2), entry min(distance, L - 1). With either, prompts take the ``mma.sync`` kernel (the tensor-memory
-    kernel has neither rule)."""
+    kernels work in base 2), entry min(distance, L - 1)."""
     if q.dtype != torch.bfloat16:
         return False
     # The entry points with a sink take it as one more argument before the stream; without a sink the plain ones are called.
@@ -309,7 +308,7 @@ def attention(out, q, cache, meta, step, spec, sink=None, chunk=0, distance_bias
     if ruled:
         extra = (sink.data_ptr() if sink is not None else None, int(chunk or 0), distance_bias2.data_ptr() if distance_bias2 is not None else None,
                  distance_bias2.shape[1] if distance_bias2 is not None else 0)
-        decode_fn, tc_fn, mma_fn = L.ti_attention_decode_biased, None, L.ti_attention_prefill_biased
+        decode_fn, tc_fn, mma_fn = L.ti_attention_decode_biased, L.ti_attention_prefill_tc_biased, L.ti_attention_prefill_biased
     else:
         decode_fn, tc_fn, mma_fn = ((L.ti_attention_decode_sink, L.ti_attention_prefill_tc_sink, L.ti_attention_prefill_sink) if sink is not None
                                     else (L.ti_attention_decode_shared, L.ti_attention_prefill_tc, L.ti_attention_prefill))
@@ -347,7 +346,7 @@ def attention(out, q, cache, meta, step, spec, sink=None, chunk=0, distance_bias
     # set-up outweighs its products (a layer of one 256-token prompt: 12 us less; level at 448 tokens; the tensor-memory
     # kernel 2 us ahead at 512, and ahead for four or more prompts of 256 tokens in one step).
     short = step.max_kv_len <= SHORT_PROMPT and step.n_tokens <= SHORT_STEP
-    rc = 2 if (short or tc_fn is None) else tc_fn(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0],
+    rc = 2 if short else tc_fn(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0],
                                        meta.block_table.data_ptr(), meta.block_table.stride(0), step.seq_slots.data_ptr(),
                                        step.cu_seqlens.data_ptr(), step.kv_lens.data_ptr(), step.n_seqs, step.n_tokens, blocks,
                                        spec.scale, spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,

@@ -161,6 +161,7 @@ _SIGNATURES_FAST["ti_attention_prefill_sink"] = _SIGNATURES_FAST["ti_attention_p
 _SIGNATURES_FAST["ti_attention_decode_sink"] = _SIGNATURES_FAST["ti_attention_decode_shared"][:-1] + [_P, _P]
 # ... and with a chunk, a bias table by distance and its length after the sink
 _SIGNATURES_FAST["ti_attention_prefill_biased"] = _SIGNATURES_FAST["ti_attention_prefill"][:-1] + [_P, _I, _P, _I, _P]
+_SIGNATURES_FAST["ti_attention_prefill_tc_biased"] = _SIGNATURES_FAST["ti_attention_prefill_tc"][:-1] + [_P, _I, _P, _I, _P]
 _SIGNATURES_FAST["ti_attention_decode_biased"] = _SIGNATURES_FAST["ti_attention_decode_shared"][:-1] + [_P, _I, _P, _I, _P]
 _SIGNATURES_FAST["ti_attention_prefill_tc_sink"] = _SIGNATURES_FAST["ti_attention_prefill_tc"][:-1] + [_P, _P]
 _SIGNATURES.update(_SIGNATURES_FAST)

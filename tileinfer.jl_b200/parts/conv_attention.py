@@ -27,7 +27,8 @@ inside the query's chunk of c positions, floor(i / c) = floor(j / c), counted fr
 learned table ``rel`` [rows, heads] adds rel[bucket(i - j), head] to the scaled score, bucket(n) = n for n < rows / 2 and
 min(rows - 1, rows / 2 + floor(ln(n / (rows / 2)) / ln(far / (rows / 2)) * (rows - rows / 2))) beyond: one row per small distance,
 logarithmic steps up to ``far``, the last row from there on. In bfloat16 attention with a chunk or a distance bias runs in the
-``mma.sync`` prompt kernel and the split-KV decode kernel (the bias comes as a table by distance), in 32-bit in the plain kernel.
+library's paged kernels (tensor-memory and ``mma.sync`` prompt kernels, split-KV decode kernel; the bias comes as a table by distance),
+in 32-bit in the plain kernel.
 
 Record: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``, ``window``, ``kv_source``, ``qk_norm_eps`` and the options
 ``value_dim``, ``conv_taps`` (0: none), ``bias``, ``out_bias``, ``row_norm``, ``head_norm``, ``norm_weight``, ``sink``, ``gate``,
